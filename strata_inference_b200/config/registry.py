@@ -44,10 +44,11 @@ def known_architectures() -> Tuple[str, ...]:
 def architecture_of(config: Mapping[str, Any]) -> Architecture:
     """Find the row for a config.json dictionary."""
     names = list(config.get("architectures") or [])
-    if config.get("model_type"):
-        names.append(config["model_type"])
+    for key in ("architecture", "model_type"):
+        if config.get(key):
+            names.append(config[key])
     if not names:
-        raise ConfigError("config.json: neither 'architectures' nor 'model_type' is given; "
+        raise ConfigError("config.json: none of 'architectures', 'architecture' and 'model_type' is given; "
                           f"known architectures: {', '.join(known_architectures())}")
     for n in names:
         if n in _ARCHITECTURES:
@@ -77,6 +78,8 @@ def spec_from_config(config: Mapping[str, Any]) -> Tuple[Any, ModelSpec]:
 def _register_builtin() -> None:
     from .gemma2 import Gemma2Config, gemma2_spec
     register_architecture(("Gemma2ForCausalLM", "gemma2"), Gemma2Config.from_dict, gemma2_spec)
+    from .karupel import KarupelConfig, karupel_spec
+    register_architecture(("Karupel", "karupel"), KarupelConfig.from_dict, karupel_spec)
 
 
 _register_builtin()

@@ -44,14 +44,19 @@ class LayerSpec:
     sites), what follows it; a part only knows its own local names (such as
     ``q_proj.weight``) and never sees the whole name table.
     ``norms`` maps the block arrangement's norm sites to norm specs.
+    ``feed_forward`` None: the layer is its mixer alone.
+    ``tensor_names`` (optional) gives, per site, stored names for the part's local names
+    where a model folder calls them otherwise ({"mixer": {"q_proj.weight": "q"}} stores the
+    mixer's ``q_proj.weight`` as ``<prefix><names["mixer"]>q``).
     """
 
     prefix: str
     block: str
     mixer: PartSpec
-    feed_forward: PartSpec
+    feed_forward: Optional[PartSpec]
     norms: Mapping[str, PartSpec]
     names: Mapping[str, str]
+    tensor_names: Mapping[str, Mapping[str, str]] = field(default_factory=dict)
 
 
 @dataclass(frozen=True)
@@ -78,6 +83,8 @@ class ModelSpec:
     head: PartSpec
     names: Mapping[str, str] = field(default_factory=dict)  # "embedding", "final_norm", "head"
     stop_tokens: Tuple[int, ...] = ()
+    # stored names for local names, per site, as in LayerSpec.tensor_names
+    tensor_names: Mapping[str, Mapping[str, str]] = field(default_factory=dict)
 
     def validate(self) -> None:
         if self.hidden_size <= 0 or self.vocab_size <= 0 or self.max_positions <= 0:

@@ -1,4 +1,4 @@
-// Embedding gather with scale, gated tanh-GELU, soft cap.
+// Embedding gather with scale, gated activations (tanh-GELU, SiLU), soft cap, row copies.
 //
 // Plain counterparts: tests/plain_gemma2.py embed(), gelu_tanh(), lm_head().
 // Reference formulas: src/backend/cpu.rs:1086-1136 (row gather),
@@ -33,12 +33,19 @@ __device__ __forceinline__ float gelu_tanh(float g) {
     return 0.5f * g * (1.0f + tanhf(c * (g + 0.044715f * g * g * g)));
 }
 
-// out[r, i] = gelu_tanh(gate(r, i)) * up(r, i).  The two halves of gate_up[r, :]
+__device__ __forceinline__ float silu_act(float g) { return g / (1.0f + expf(-g)); }
+
+enum { ACT_GELU_TANH = 0, ACT_SILU = 1 };
+__device__ __forceinline__ float gate_act(float g, int act) {
+    return act == ACT_SILU ? silu_act(g) : gelu_tanh(g);
+}
+
+// out[r, i] = act(gate(r, i)) * up(r, i).  The two halves of gate_up[r, :]
 // are laid out either as [all gates | all ups] (group == 0) or in groups of
 // `group` gates followed by the `group` matching ups.
 template <typename T>
 __global__ void gelu_mul_kernel(const T* __restrict__ gate_up, T* __restrict__ out, int inter,
-                                int group, size_t total) {
+                                int group, size_t total, int act) {
     for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total;
          idx += (size_t)gridDim.x * blockDim.x) {
         const size_t r = idx / inter;
@@ -47,7 +54,7 @@ __global__ void gelu_mul_kernel(const T* __restrict__ gate_up, T* __restrict__ o
         const int gi = group ? (i / group) * 2 * group + i % group : i;
         const int ui = group ? gi + group : inter + i;
         const float g = to_f32(row[gi]), u = to_f32(row[ui]);
-        out[idx] = from_f32<T>(gelu_tanh(g) * u);
+        out[idx] = from_f32<T>(gate_act(g, act) * u);
     }
 }
 
@@ -55,7 +62,7 @@ __global__ void gelu_mul_kernel(const T* __restrict__ gate_up, T* __restrict__ o
 // 8 ups) and gives 16 contiguous bytes of output; one thread per group, every
 // access 16 bytes wide.
 __global__ void gelu_mul_group8_bf16_kernel(const uint4* __restrict__ gate_up,
-                                            uint4* __restrict__ out, size_t groups) {
+                                            uint4* __restrict__ out, size_t groups, int act) {
     for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < groups;
          i += (size_t)gridDim.x * blockDim.x) {
         const uint4 gv = gate_up[2 * i], uv = gate_up[2 * i + 1];
@@ -65,17 +72,18 @@ __global__ void gelu_mul_group8_bf16_kernel(const uint4* __restrict__ gate_up,
         for (int k = 0; k < 4; ++k) {
             const float g0 = __uint_as_float(gw[k] << 16), g1 = __uint_as_float(gw[k] & 0xffff0000u);
             const float u0 = __uint_as_float(uw[k] << 16), u1 = __uint_as_float(uw[k] & 0xffff0000u);
-            const __nv_bfloat162 o = __floats2bfloat162_rn(gelu_tanh(g0) * u0, gelu_tanh(g1) * u1);
+            const __nv_bfloat162 o = __floats2bfloat162_rn(gate_act(g0, act) * u0, gate_act(g1, act) * u1);
             ow[k] = *reinterpret_cast<const uint32_t*>(&o);
         }
         out[i] = make_uint4(ow[0], ow[1], ow[2], ow[3]);
     }
 }
 
-SIB_EXPORT int sib_gelu_mul(const void* gate_up, void* out, int dtype, int rows, int inter,
-                            int group, void* stream) {
+SIB_EXPORT int sib_gated_mul(const void* gate_up, void* out, int dtype, int rows, int inter,
+                             int group, int act, void* stream) {
     if (rows == 0) return 0;
     SIB_REQUIRE(rows > 0 && inter > 0, "gelu_mul: rows=%d inter=%d", rows, inter);
+    SIB_REQUIRE(act == ACT_GELU_TANH || act == ACT_SILU, "gelu_mul: unknown activation %d", act);
     SIB_REQUIRE(group >= 0 && (group == 0 || inter % group == 0),
                 "gelu_mul: %d columns do not come in groups of %d", inter, group);
     const size_t total = (size_t)rows * inter;
@@ -85,13 +93,47 @@ SIB_EXPORT int sib_gelu_mul(const void* gate_up, void* out, int dtype, int rows,
         const size_t want = (groups + 255) / 256;
         const int blocks = (int)(want < 148 * 32 ? want : 148 * 32);
         gelu_mul_group8_bf16_kernel<<<blocks, 256, 0, (cudaStream_t)stream>>>(
-            (const uint4*)gate_up, (uint4*)out, groups);
+            (const uint4*)gate_up, (uint4*)out, groups, act);
         return sib_check_launch("gelu_mul");
     }
     const int blocks = (int)((total + 255) / 256 < 148 * 16 ? (total + 255) / 256 : 148 * 16);
     SIB_DISPATCH_DTYPE(dtype, (gelu_mul_kernel<T><<<blocks, 256, 0, (cudaStream_t)stream>>>(
-                                  (const T*)gate_up, (T*)out, inter, group, total)));
+                                  (const T*)gate_up, (T*)out, inter, group, total, act)));
     return sib_check_launch("gelu_mul");
+}
+
+SIB_EXPORT int sib_gelu_mul(const void* gate_up, void* out, int dtype, int rows, int inter,
+                            int group, void* stream) {
+    return sib_gated_mul(gate_up, out, dtype, rows, inter, group, ACT_GELU_TANH, stream);
+}
+
+// out = x in another element type (the 32-bit stream as activations).
+template <typename Tin, typename Tout>
+__global__ void cast_rows_kernel(const Tin* __restrict__ x, Tout* __restrict__ out, size_t total) {
+    pdl_trigger();
+    pdl_wait();
+    for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total;
+         idx += (size_t)gridDim.x * blockDim.x)
+        out[idx] = from_f32<Tout>(to_f32(x[idx]));
+}
+
+SIB_EXPORT int sib_cast_rows(const void* x, int in_dtype, void* out, int out_dtype, long long total,
+                             void* stream) {
+    if (total == 0) return 0;
+    SIB_REQUIRE(total > 0, "cast_rows: %lld elements", total);
+    const long long want = (total + 255) / 256;
+    const int blocks = (int)(want < 148 * 16 ? want : 148 * 16);
+    cudaStream_t s = (cudaStream_t)stream;
+#define GO(TIN, TOUT) \
+    sib_launch_chained(cast_rows_kernel<TIN, TOUT>, dim3(blocks), dim3(256), 0, s, (const TIN*)x, \
+                       (TOUT*)out, (size_t)total)
+    if (in_dtype == SIB_F32 && out_dtype == SIB_F32) GO(float, float);
+    else if (in_dtype == SIB_F32 && out_dtype == SIB_BF16) GO(float, __nv_bfloat16);
+    else if (in_dtype == SIB_BF16 && out_dtype == SIB_BF16) GO(__nv_bfloat16, __nv_bfloat16);
+    else if (in_dtype == SIB_BF16 && out_dtype == SIB_F32) GO(__nv_bfloat16, float);
+    else SIB_REQUIRE(false, "cast_rows: unknown element types %d -> %d", in_dtype, out_dtype);
+#undef GO
+    return sib_check_launch("cast_rows");
 }
 
 // x = cap * tanh(x / cap), in place, 32-bit.

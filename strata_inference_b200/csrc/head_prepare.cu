@@ -1,0 +1,193 @@
+// What lies between the q|k|v product and the attention kernel for mixers whose heads are
+// worked on first, and what lies between the attention kernel and the output product:
+//
+//   head_prepare   per row and head, in 32-bit:
+//       x  = proj + bias                                   (bias optional)
+//       q, k: x <- x / sqrt(mean(x^2) + eps) * w           (w optional: no norm without it)
+//       q, k: the first `rot` dimensions rotated in half-split pairs (i, i + rot/2) by
+//             the angle pos * inv_freq[i]; the rest pass
+//       v:    v <- (1 - lambda) v + lambda v_first         (v_first optional)
+//     q, k and v go to a packed buffer whose heads are all `pad` wide (key width and value
+//     width may differ: the narrower one is filled up with zeros, which changes neither a
+//     score nor a weighted sum), and k and v also into the paged cache of that width.
+//
+//   head_gate      y[r, h, :vd] = o[r, h, :vd] * sigmoid(gate[r, h])    (gate optional)
+//     which also drops the filled-up columns again.
+//
+// Plain counterpart: tests/plain_karupel.py attention_mixer().
+#include "common.cuh"
+
+struct HeadPrepareArgs {
+    const void* proj;          // [rows, proj_stride]: q heads | k heads | v heads | ...
+    void* qkv;                 // [rows, (n_heads + 2 n_kv) * pad]
+    const float* bias;         // [n_heads * kd + n_kv * kd + n_kv * vd] or null
+    const float* q_gain;       // [kd] or null
+    const float* k_gain;       // [kd] or null
+    const float* inv_freq;     // [rot / 2] or null
+    const void* v_first;       // row r, kv head g at v_first + r * v_first_stride + g * pad; or null
+    const float* lambda;       // one value on the device (with v_first)
+    const int* row_pos;
+    const int* row_seq;
+    const int* seq_slot;
+    const int* seq_end;
+    void* k_pool;              // [pages, n_kv, page_tokens, pad]; null: nothing is stored
+    void* v_pool;
+    const int* page_table;
+    long long proj_stride, v_first_stride;
+    int n_heads, n_kv, kd, vd, pad, rot;
+    int max_pages, page_tokens, ring_tokens;
+    float eps;
+};
+
+// One warp per (row, head unit); a block takes 4 units of one row.
+template <typename T>
+__global__ void __launch_bounds__(128) head_prepare_kernel(HeadPrepareArgs p) {
+    extern __shared__ float staged[];          // [4][pad]
+    pdl_trigger();
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int r = blockIdx.x;
+    const int unit = blockIdx.y * 4 + warp;
+    const int units = p.n_heads + 2 * p.n_kv;
+    if (unit >= units) return;
+    float* mine = staged + (size_t)warp * p.pad;
+    const bool is_q = unit < p.n_heads;
+    const bool is_v = unit >= p.n_heads + p.n_kv;
+    const int width = is_v ? p.vd : p.kd;
+    // where the unit's values start in a row of proj (and in bias)
+    const int col = is_q ? unit * p.kd
+                         : !is_v ? p.n_heads * p.kd + (unit - p.n_heads) * p.kd
+                                 : (p.n_heads + p.n_kv) * p.kd + (unit - p.n_heads - p.n_kv) * p.vd;
+    const int pos = p.row_pos[r];
+    T* dst = nullptr;
+    if (!is_q && p.k_pool) {
+        const int b = p.row_seq[r];
+        const int slot = p.seq_slot[b];
+        bool keep = slot >= 0;               // (a filling row's sequence holds no slot)
+        int cell = pos;
+        if (keep && p.ring_tokens > 0) {
+            keep = pos >= p.seq_end[b] - p.ring_tokens;
+            cell = pos % p.ring_tokens;
+        }
+        if (keep) {
+            const int page = p.page_table[(size_t)slot * p.max_pages + cell / p.page_tokens];
+            const int g = is_v ? unit - p.n_heads - p.n_kv : unit - p.n_heads;
+            T* pool = (T*)(is_v ? p.v_pool : p.k_pool);
+            dst = pool + (((size_t)page * p.n_kv + g) * p.page_tokens + cell % p.page_tokens) * p.pad;
+        }
+    }
+    pdl_wait();
+    const T* src = (const T*)p.proj + (size_t)r * p.proj_stride + col;
+    float ss = 0.f;
+    for (int d = lane; d < width; d += 32) {
+        float x = to_f32(src[d]);
+        if (p.bias) x += p.bias[col + d];
+        mine[d] = x;
+        ss += x * x;
+    }
+    T* out = (T*)p.qkv + (size_t)r * units * p.pad + (size_t)unit * p.pad;
+    if (is_v) {
+        const T* first = p.v_first
+            ? (const T*)p.v_first + (size_t)r * p.v_first_stride + (size_t)(unit - p.n_heads - p.n_kv) * p.pad
+            : nullptr;
+        const float lam = first ? *p.lambda : 0.f;
+        for (int d = lane; d < p.pad; d += 32) {
+            float x = 0.f;
+            if (d < width) {
+                x = mine[d];
+                if (first) x = (1.f - lam) * x + lam * to_f32(first[d]);
+            }
+            const T y = from_f32<T>(x);
+            out[d] = y;
+            if (dst) dst[d] = y;
+        }
+        return;
+    }
+    const float* gain = is_q ? p.q_gain : p.k_gain;
+    float inv = 1.f;
+    if (gain) inv = 1.0f / sqrtf(warp_sum(ss) / (float)width + p.eps);
+    __syncwarp();
+    if (gain)
+        for (int d = lane; d < width; d += 32) mine[d] = mine[d] * inv * gain[d];
+    __syncwarp();
+    const int half = p.inv_freq ? p.rot / 2 : 0;
+    for (int d = lane; d < p.pad; d += 32) {
+        float x = 0.f;
+        if (d < width) {
+            x = mine[d];
+            if (d < 2 * half) {
+                const int i = d < half ? d : d - half;
+                const float ang = (float)pos * p.inv_freq[i];
+                const float c = cosf(ang), s = sinf(ang);
+                x = d < half ? x * c - mine[d + half] * s : x * c + mine[d - half] * s;
+            }
+        }
+        const T y = from_f32<T>(x);
+        out[d] = y;
+        if (dst) dst[d] = y;
+    }
+}
+
+SIB_EXPORT int sib_head_prepare(
+    const void* proj, long long proj_stride, void* qkv, int dtype, const float* bias,
+    const float* q_gain, const float* k_gain, float eps, const float* inv_freq, int rot,
+    const void* v_first, long long v_first_stride, const float* lambda, const int* row_pos,
+    const int* row_seq, const int* seq_slot, const int* seq_end, void* k_pool, void* v_pool,
+    const int* page_table, int max_pages, int page_tokens, int ring_tokens, int rows, int n_heads,
+    int n_kv, int kd, int vd, int pad, void* stream) {
+    if (rows == 0) return 0;
+    SIB_REQUIRE(rows > 0 && n_heads > 0 && n_kv >= 0 && kd > 0 && vd > 0,
+                "head_prepare: rows=%d heads=%d kv_heads=%d key width=%d value width=%d", rows,
+                n_heads, n_kv, kd, vd);
+    SIB_REQUIRE(pad >= kd && pad >= vd, "head_prepare: heads of %d and %d do not fit a width of %d",
+                kd, vd, pad);
+    SIB_REQUIRE(rot >= 0 && rot % 2 == 0 && rot <= kd && (rot == 0 || inv_freq != nullptr),
+                "head_prepare: %d rotated dimensions of %d", rot, kd);
+    SIB_REQUIRE(row_pos != nullptr, "head_prepare: positions are needed");
+    SIB_REQUIRE(k_pool == nullptr || (v_pool && page_table && row_seq && seq_slot && seq_end &&
+                                      page_tokens > 0 && max_pages > 0),
+                "head_prepare: incomplete cache description");
+    SIB_REQUIRE(v_first == nullptr || lambda != nullptr, "head_prepare: mixing values needs lambda");
+    HeadPrepareArgs p{proj, qkv, bias, q_gain, k_gain, rot ? inv_freq : nullptr, v_first, lambda,
+                      row_pos, row_seq, seq_slot, seq_end, k_pool, v_pool, page_table, proj_stride,
+                      v_first_stride, n_heads, n_kv, kd, vd, pad, rot, max_pages, page_tokens,
+                      ring_tokens, eps};
+    const int units = n_heads + 2 * n_kv;
+    const size_t smem = (size_t)4 * pad * sizeof(float);
+    SIB_REQUIRE(smem <= 48 * 1024, "head_prepare: heads of %d are too wide", pad);
+    SIB_REQUIRE(rows < 65536 * 32767ll && (units + 3) / 4 < 65536, "head_prepare: too many rows");
+    SIB_DISPATCH_DTYPE(dtype, sib_launch_chained(head_prepare_kernel<T>, dim3(rows, (units + 3) / 4),
+                                                 dim3(128), smem, (cudaStream_t)stream, p));
+    return sib_check_launch("head_prepare");
+}
+
+// y[r, h * vd + e] = o[r, h * pad + e] * sigmoid(gate[r * gate_stride + h])
+template <typename T>
+__global__ void head_gate_kernel(const T* __restrict__ o, const T* __restrict__ gate,
+                                 long long gate_stride, T* __restrict__ y, int n_heads, int vd,
+                                 int pad, size_t total) {
+    pdl_trigger();
+    pdl_wait();
+    for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total;
+         idx += (size_t)gridDim.x * blockDim.x) {
+        const size_t r = idx / ((size_t)n_heads * vd);
+        const int rest = (int)(idx - r * (size_t)n_heads * vd);
+        const int h = rest / vd, e = rest - h * vd;
+        float x = to_f32(o[(r * n_heads + h) * (size_t)pad + e]);
+        if (gate) x *= 1.0f / (1.0f + expf(-to_f32(gate[r * gate_stride + h])));
+        y[idx] = from_f32<T>(x);
+    }
+}
+
+SIB_EXPORT int sib_head_gate(const void* o, const void* gate, long long gate_stride, void* y,
+                             int dtype, int rows, int n_heads, int vd, int pad, void* stream) {
+    if (rows == 0) return 0;
+    SIB_REQUIRE(rows > 0 && n_heads > 0 && vd > 0 && pad >= vd,
+                "head_gate: rows=%d heads=%d width=%d of %d", rows, n_heads, vd, pad);
+    const size_t total = (size_t)rows * n_heads * vd;
+    const size_t want = (total + 255) / 256;
+    const int blocks = (int)(want < 148 * 16 ? want : 148 * 16);
+    SIB_DISPATCH_DTYPE(dtype, sib_launch_chained(head_gate_kernel<T>, dim3(blocks), dim3(256), 0,
+                                                 (cudaStream_t)stream, (const T*)o, (const T*)gate,
+                                                 gate_stride, (T*)y, n_heads, vd, pad, total));
+    return sib_check_launch("head_gate");
+}

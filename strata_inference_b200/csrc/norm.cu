@@ -35,7 +35,7 @@ __global__ void rms_norm_kernel(const Tin* __restrict__ x, const int* __restrict
 }
 
 // h[r, :] += post_gain ? rms(a[r, :], post_gain) : a[r, :]
-// out[r, :] = rms(h[r, :], pre_gain)            (only if pre_gain)
+// out[r, :] = pre_gain ? rms(h[r, :], pre_gain) : h[r, :]      (only if out)
 // h is the 32-bit residual stream; a and out have the activation type.
 template <typename T>
 __global__ void add_rms_norm_kernel(const T* __restrict__ a, const float* __restrict__ post_gain,
@@ -66,11 +66,14 @@ __global__ void add_rms_norm_kernel(const T* __restrict__ a, const float* __rest
         row[c] = v;
         ss2 += v * v;
     }
-    if (!pre_gain) return;
-    ss2 = block_sum(ss2, scratch);
-    const float inv2 = 1.0f / sqrtf(ss2 / (float)hidden + pre_eps);
+    if (!out) return;
+    float inv2 = 1.f;
+    if (pre_gain) {
+        ss2 = block_sum(ss2, scratch);
+        inv2 = 1.0f / sqrtf(ss2 / (float)hidden + pre_eps);
+    }
     for (int c = threadIdx.x; c < hidden; c += blockDim.x)
-        out[base + c] = from_f32<T>(row[c] * inv2 * pre_gain[c]);
+        out[base + c] = from_f32<T>(pre_gain ? row[c] * inv2 * pre_gain[c] : row[c]);
 }
 
 // The same for bfloat16 activations and a hidden size in whole groups of 8: every
@@ -117,16 +120,22 @@ __global__ void add_rms_norm_bf16_kernel(const __nv_bfloat16* __restrict__ a,
         *reinterpret_cast<float4*>(row + 4 * v) = hv;
         ss2 += hv.x * hv.x + hv.y * hv.y + hv.z * hv.z + hv.w * hv.w;
     }
-    if (!pre_gain) return;
-    ss2 = block_sum(ss2, scratch);
-    const float inv2 = 1.0f / sqrtf(ss2 / (float)hidden + pre_eps);
+    if (!out) return;
+    float inv2 = 1.f;
+    if (pre_gain) {
+        ss2 = block_sum(ss2, scratch);
+        inv2 = 1.0f / sqrtf(ss2 / (float)hidden + pre_eps);
+    } else {
+        __syncthreads();   // the next pass reads the row in another order
+    }
     for (int v = threadIdx.x; v < groups; v += blockDim.x) {
         uint32_t w[4];
 #pragma unroll
         for (int k = 0; k < 4; ++k) {
             const int c = 8 * v + 2 * k;
-            const __nv_bfloat162 o = __floats2bfloat162_rn(row[c] * inv2 * pre_gain[c],
-                                                           row[c + 1] * inv2 * pre_gain[c + 1]);
+            const float g0 = pre_gain ? pre_gain[c] : 1.f, g1 = pre_gain ? pre_gain[c + 1] : 1.f;
+            const __nv_bfloat162 o = __floats2bfloat162_rn(row[c] * inv2 * g0,
+                                                           row[c + 1] * inv2 * g1);
             w[k] = *reinterpret_cast<const uint32_t*>(&o);
         }
         *reinterpret_cast<uint4*>(out + base + 8 * v) = make_uint4(w[0], w[1], w[2], w[3]);
@@ -184,13 +193,14 @@ add_rms_norm_bf16_warp_kernel(const __nv_bfloat16* __restrict__ a, const float* 
 #pragma unroll
         for (int e = 0; e < 8; ++e) ss2 += v[i][e] * v[i][e];
     }
-    if (!pre_gain) return;
-    const float inv2 = 1.0f / sqrtf(warp_sum(ss2) / (float)hidden + pre_eps);
+    if (!out) return;
+    const float inv2 = pre_gain ? 1.0f / sqrtf(warp_sum(ss2) / (float)hidden + pre_eps) : 1.f;
+    const float4 ones = make_float4(1.f, 1.f, 1.f, 1.f);
 #pragma unroll
     for (int i = 0; i < NG; ++i) {
         const int c = 8 * (lane + 32 * i);
-        const float4 g0 = *reinterpret_cast<const float4*>(pre_gain + c);
-        const float4 g1 = *reinterpret_cast<const float4*>(pre_gain + c + 4);
+        const float4 g0 = pre_gain ? *reinterpret_cast<const float4*>(pre_gain + c) : ones;
+        const float4 g1 = pre_gain ? *reinterpret_cast<const float4*>(pre_gain + c + 4) : ones;
         const float g[8] = {g0.x, g0.y, g0.z, g0.w, g1.x, g1.y, g1.z, g1.w};
         uint32_t w[4];
 #pragma unroll
@@ -255,11 +265,14 @@ add_rms_norm_bf16_group_kernel(const __nv_bfloat16* __restrict__ a, const float*
         *reinterpret_cast<float4*>(h + base) = h0;
         *reinterpret_cast<float4*>(h + base + 4) = h1;
     }
-    if (!pre_gain) return;
-    float ss2 = h0.x * h0.x + h0.y * h0.y + h0.z * h0.z + h0.w * h0.w +
-                h1.x * h1.x + h1.y * h1.y + h1.z * h1.z + h1.w * h1.w;
-    ss2 = block_sum(ss2, scratch);
-    const float inv2 = 1.0f / sqrtf(ss2 / (float)hidden + pre_eps);
+    if (!out) return;
+    float inv2 = 1.f;
+    if (pre_gain) {
+        float ss2 = h0.x * h0.x + h0.y * h0.y + h0.z * h0.z + h0.w * h0.w +
+                    h1.x * h1.x + h1.y * h1.y + h1.z * h1.z + h1.w * h1.w;
+        ss2 = block_sum(ss2, scratch);
+        inv2 = 1.0f / sqrtf(ss2 / (float)hidden + pre_eps);
+    }
     if (live) {
         const __nv_bfloat162 o0 = __floats2bfloat162_rn(h0.x * inv2 * qg0.x, h0.y * inv2 * qg0.y);
         const __nv_bfloat162 o1 = __floats2bfloat162_rn(h0.z * inv2 * qg0.z, h0.w * inv2 * qg0.w);

@@ -14,7 +14,7 @@ import torch
 from ..cache.paged import CacheNeed
 from ..config.spec import ModelSpec, PartSpec
 from ..parts import registry as parts
-from ..weights.arena import DictSource, Resident, WeightArena, resident_of
+from ..weights.arena import DictSource, Piece, Resident, WeightArena, resident_of
 from ..weights.loader import TensorDecl, check_table
 
 
@@ -23,58 +23,47 @@ def _sub(weights: Mapping[str, torch.Tensor], prefix: str) -> Dict[str, torch.Te
 
 
 def expected_tensors(spec: ModelSpec) -> Dict[str, TensorDecl]:
-    """Every tensor the model needs, by full name, from the parts' declarations."""
-    H, V = spec.hidden_size, spec.vocab_size
+    """Every tensor the model needs, by full (stored) name, from the parts' declarations."""
     out: Dict[str, TensorDecl] = {}
-
-    def add(prefix: str, decls: Mapping[str, TensorDecl]) -> None:
-        for name, d in decls.items():
-            out[prefix + name] = d
-
-    add(spec.names["embedding"],
-        parts.part_class("embedding", spec.embedding.kind).tensors(spec.embedding.params, H, V))
-    for layer in spec.layers:
-        add(layer.prefix + layer.names["mixer"],
-            parts.part_class("mixer", layer.mixer.kind).tensors(layer.mixer.params, H))
-        add(layer.prefix + layer.names["feed_forward"],
-            parts.part_class("feed_forward", layer.feed_forward.kind).tensors(
-                layer.feed_forward.params, H))
-        for site, norm in layer.norms.items():
-            add(layer.prefix + layer.names[site],
-                parts.part_class("norm", norm.kind).tensors(norm.params, H))
-    add(spec.names["final_norm"],
-        parts.part_class("norm", spec.final_norm.kind).tensors(spec.final_norm.params, H))
-    add(spec.names["head"],
-        parts.part_class("head", spec.head.kind).tensors(spec.head.params, H, V))
+    for prefix, cls, args, stored in _sites(spec):
+        for name, d in cls.tensors(*args).items():
+            out[prefix + stored.get(name, name)] = d
     return out
 
 
 def _sites(spec: ModelSpec):
-    """(prefix, part class, arguments of its tensors()/resident()) of every part that
-    has tensors, in the order the model is built."""
+    """(prefix, part class, arguments of its tensors()/resident(), stored names for local
+    names) of every part that has tensors, in the order the model is built."""
     H, V = spec.hidden_size, spec.vocab_size
     yield (spec.names["embedding"], parts.part_class("embedding", spec.embedding.kind),
-           (spec.embedding.params, H, V))
+           (spec.embedding.params, H, V), spec.tensor_names.get("embedding", {}))
     for layer in spec.layers:
         yield (layer.prefix + layer.names["mixer"], parts.part_class("mixer", layer.mixer.kind),
-               (layer.mixer.params, H))
-        yield (layer.prefix + layer.names["feed_forward"],
-               parts.part_class("feed_forward", layer.feed_forward.kind),
-               (layer.feed_forward.params, H))
+               (layer.mixer.params, H), layer.tensor_names.get("mixer", {}))
+        if layer.feed_forward is not None:
+            yield (layer.prefix + layer.names["feed_forward"],
+                   parts.part_class("feed_forward", layer.feed_forward.kind),
+                   (layer.feed_forward.params, H), layer.tensor_names.get("feed_forward", {}))
         for site, norm in layer.norms.items():
             yield (layer.prefix + layer.names[site], parts.part_class("norm", norm.kind),
-                   (norm.params, H))
+                   (norm.params, H), layer.tensor_names.get(site, {}))
     yield (spec.names["final_norm"], parts.part_class("norm", spec.final_norm.kind),
-           (spec.final_norm.params, H))
-    yield (spec.names["head"], parts.part_class("head", spec.head.kind), (spec.head.params, H, V))
+           (spec.final_norm.params, H), spec.tensor_names.get("final_norm", {}))
+    yield (spec.names["head"], parts.part_class("head", spec.head.kind), (spec.head.params, H, V),
+           spec.tensor_names.get("head", {}))
 
 
 def resident_plan(spec: ModelSpec) -> Dict[str, Tuple[Resident, str]]:
     """Every tensor the model keeps on the device, by full name, with the prefix of
-    the stored tensors it is put together from."""
+    the stored tensors it is put together from; the pieces name their stored tensors as
+    the model folder does."""
     plan: Dict[str, Tuple[Resident, str]] = {}
-    for prefix, cls, args in _sites(spec):
+    for prefix, cls, args, stored in _sites(spec):
         for name, res in resident_of(cls, cls.tensors(*args), *args).items():
+            if stored:
+                res = Resident(res.shape, res.dtype, tuple(
+                    Piece(stored.get(q.source, q.source), q.row_offset, q.group, q.group_stride)
+                    for q in res.pieces), res.offset)
             plan[prefix + name] = (res, prefix)
     return plan
 
@@ -115,9 +104,11 @@ class DecoderModel:
         for layer in spec.layers:
             mixer = parts.part_class("mixer", layer.mixer.kind)(
                 layer.mixer.params, H, _sub(weights, layer.prefix + layer.names["mixer"]), rt)
-            ff = parts.part_class("feed_forward", layer.feed_forward.kind)(
-                layer.feed_forward.params, H,
-                _sub(weights, layer.prefix + layer.names["feed_forward"]), rt)
+            ff = None
+            if layer.feed_forward is not None:
+                ff = parts.part_class("feed_forward", layer.feed_forward.kind)(
+                    layer.feed_forward.params, H,
+                    _sub(weights, layer.prefix + layer.names["feed_forward"]), rt)
             norms = {site: parts.part_class("norm", n.kind)(
                 n.params, H, _sub(weights, layer.prefix + layer.names[site]), rt)
                 for site, n in layer.norms.items()}

@@ -20,6 +20,8 @@ import torch
 F32, BF16 = 0, 1
 EPI_NONE, EPI_SOFTCAP, EPI_GEGLU = 0, 1, 2
 ROPE_HALF_SPLIT, ROPE_INTERLEAVED = 0, 1
+ACT_GELU_TANH, ACT_SILU = 0, 1          # of the gated feed-forward
+GATE_SILU, GATE_SIGMOID = 0, 1          # of head_norm_gate
 
 _lib = None
 
@@ -286,17 +288,30 @@ def randn_fill(dst: torch.Tensor, rows: int, cols: int, group: int, group_stride
         c_int(BF16 if stored_dtype == torch.bfloat16 else F32), _stream()))
 
 
-@_timed(lambda gate_up, out, group=0: ("gelu_mul", _nbytes(gate_up, out), 0))
-def gelu_mul(gate_up: torch.Tensor, out: torch.Tensor, group: int = 0) -> torch.Tensor:
-    """out[r, i] = gelu_tanh(gate(r, i)) * up(r, i); gate_up rows are [gates | ups]
-    (group 0) or groups of ``group`` gates followed by their ups."""
+@_timed(lambda gate_up, out, group=0, act=ACT_GELU_TANH: ("gelu_mul", _nbytes(gate_up, out), 0))
+def gelu_mul(gate_up: torch.Tensor, out: torch.Tensor, group: int = 0,
+             act: int = ACT_GELU_TANH) -> torch.Tensor:
+    """out[r, i] = act(gate(r, i)) * up(r, i), act the tanh-GELU or SiLU; gate_up rows are
+    [gates | ups] (group 0) or groups of ``group`` gates followed by their ups."""
     rows, inter = out.shape
     _want(gate_up, out.dtype, "gate_up")
     _want(out, out.dtype, "out")
     if tuple(gate_up.shape) != (rows, 2 * inter):
         raise KernelError("gelu_mul: gate_up must be [rows, 2 * intermediate]")
-    _check(library().sib_gelu_mul(_ptr(gate_up), _ptr(out), _code(out.dtype), c_int(rows),
-                                  c_int(inter), c_int(group), _stream()))
+    _check(library().sib_gated_mul(_ptr(gate_up), _ptr(out), _code(out.dtype), c_int(rows),
+                                   c_int(inter), c_int(group), c_int(act), _stream()))
+    return out
+
+
+@_timed(lambda x, out: ("cast_rows", _nbytes(x, out), 0))
+def cast_rows(x: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
+    """out = x in out's element type (the 32-bit stream as activations)."""
+    _want(x, x.dtype, "x")
+    _want(out, out.dtype, "out")
+    if x.numel() != out.numel():
+        raise KernelError("cast_rows: x and out differ in size")
+    _check(library().sib_cast_rows(_ptr(x), _code(x.dtype), _ptr(out), _code(out.dtype),
+                                   c_longlong(x.numel()), _stream()))
     return out
 
 
@@ -383,6 +398,208 @@ def rope_store(qkv: torch.Tensor, row_pos, row_seq, seq_slot, seq_end,
         _ptr(inv_freq), c_int(rotary_dim), c_int(style), _ptr(k_pool), _ptr(v_pool),
         _ptr(page_table), c_int(max_pages), c_int(page_tokens), c_int(ring_tokens), c_int(rows),
         c_int(n_heads), c_int(n_kv), c_int(head_dim), _stream()))
+
+
+@_timed(lambda proj, qkv, *a, **kw: ("head_prepare", _nbytes(proj, qkv), 0))
+def head_prepare(proj: torch.Tensor, qkv: torch.Tensor, bias: Optional[torch.Tensor],
+                 q_gain: Optional[torch.Tensor], k_gain: Optional[torch.Tensor], eps: float,
+                 inv_freq: Optional[torch.Tensor], rotary_dim: int,
+                 v_first: Optional[torch.Tensor], lam: Optional[torch.Tensor], row_pos, row_seq,
+                 seq_slot, seq_end, k_pool: Optional[torch.Tensor], v_pool: Optional[torch.Tensor],
+                 page_table: Optional[torch.Tensor], page_tokens: int, ring_tokens: int,
+                 n_heads: int, n_kv: int, key_dim: int, value_dim: int, pad: int) -> torch.Tensor:
+    """From a projected row ``[q heads | k heads | v heads | ...]`` to the packed q|k|v rows
+    the attention kernels read, heads ``pad`` wide (csrc/head_prepare.cu): bias, per-head RMS
+    norm of q and k with a gain, partial rotation, values mixed with ``v_first`` (a view
+    ``[rows, n_kv * pad]`` of an earlier layer's packed rows) by ``lam``, and k and v written
+    into the paged cache."""
+    rows = proj.shape[0]
+    _want(proj, qkv.dtype, "proj", contiguous=False)
+    _want(qkv, qkv.dtype, "qkv")
+    need = n_heads * key_dim + n_kv * (key_dim + value_dim)
+    if proj.stride(1) != 1 or proj.shape[1] < need:
+        raise KernelError("head_prepare: a projected row must hold q, k and v side by side")
+    if tuple(qkv.shape) != (rows, (n_heads + 2 * n_kv) * pad):
+        raise KernelError("head_prepare: the packed rows do not fit the head counts")
+    for t, n, nm in ((bias, need, "bias"), (q_gain, key_dim, "q_gain"), (k_gain, key_dim, "k_gain"),
+                     (inv_freq, rotary_dim // 2, "inv_freq"), (lam, 1, "lam")):
+        if t is not None:
+            _want(t, torch.float32, nm)
+            if t.numel() != n:
+                raise KernelError(f"head_prepare: {nm} has {t.numel()} values, expected {n}")
+    v_stride = 0
+    if v_first is not None:
+        _want(v_first, qkv.dtype, "v_first", contiguous=False)
+        if v_first.stride(1) != 1 or tuple(v_first.shape) != (rows, n_kv * pad) or lam is None:
+            raise KernelError("head_prepare: v_first must be [rows, kv heads x width] with lam")
+        v_stride = v_first.stride(0)
+    max_pages = 0
+    if k_pool is not None:
+        _want(k_pool, qkv.dtype, "k_pool")
+        _want(v_pool, qkv.dtype, "v_pool")
+        _want(page_table, torch.int32, "page_table")
+        max_pages = page_table.shape[1]
+        want = (n_kv, page_tokens, pad)
+        if tuple(k_pool.shape[1:]) != want or tuple(v_pool.shape[1:]) != want:
+            raise KernelError("head_prepare: pool layout must be [pages, kv_heads, page_tokens, width]")
+    _check(library().sib_head_prepare(
+        _ptr(proj), c_longlong(proj.stride(0)), _ptr(qkv), _code(qkv.dtype), _ptr(bias),
+        _ptr(q_gain), _ptr(k_gain), c_float(eps), _ptr(inv_freq), c_int(rotary_dim if inv_freq is not None else 0),
+        _ptr(v_first), c_longlong(v_stride), _ptr(lam), _ptr(row_pos), _ptr(row_seq), _ptr(seq_slot),
+        _ptr(seq_end), _ptr(k_pool), _ptr(v_pool), _ptr(page_table), c_int(max_pages),
+        c_int(page_tokens), c_int(ring_tokens), c_int(rows), c_int(n_heads), c_int(n_kv),
+        c_int(key_dim), c_int(value_dim), c_int(pad), _stream()))
+    return qkv
+
+
+@_timed(lambda o, gate, y, *a: ("head_gate", _nbytes(o, y), 0))
+def head_gate(o: torch.Tensor, gate: Optional[torch.Tensor], y: torch.Tensor, n_heads: int,
+              value_dim: int, pad: int) -> torch.Tensor:
+    """y[r, h, :] = o[r, h, :value_dim] * sigmoid(gate[r, h]); ``o`` has heads ``pad`` wide,
+    ``gate`` is a view ``[rows, n_heads]`` (None: no gate, only the narrowing)."""
+    rows = o.shape[0]
+    _want(o, y.dtype, "o")
+    _want(y, y.dtype, "y")
+    if tuple(o.shape) != (rows, n_heads * pad) or tuple(y.shape) != (rows, n_heads * value_dim):
+        raise KernelError("head_gate: shapes do not fit the head counts")
+    stride = 0
+    if gate is not None:
+        _want(gate, y.dtype, "gate", contiguous=False)
+        if tuple(gate.shape) != (rows, n_heads) or gate.stride(1) != 1:
+            raise KernelError("head_gate: one gate value per row and head")
+        stride = gate.stride(0)
+    _check(library().sib_head_gate(_ptr(o), _ptr(gate), c_longlong(stride), _ptr(y), _code(y.dtype),
+                                   c_int(rows), c_int(n_heads), c_int(value_dim), c_int(pad),
+                                   _stream()))
+    return y
+
+
+def _f32(t: Optional[torch.Tensor], n: int, name: str) -> None:
+    if t is None:
+        raise KernelError(f"{name} is needed")
+    _want(t, torch.float32, name)
+    if t.numel() != n:
+        raise KernelError(f"{name} has {t.numel()} values, expected {n}")
+
+
+@_timed(lambda proj, *a, **kw: ("delta_prepare", 3 * _nbytes(proj), 0))
+def delta_prepare(proj: torch.Tensor, conv_w: torch.Tensor, a_log: torch.Tensor,
+                  dt_bias: torch.Tensor, state: torch.Tensor, hist_offset: int, qn: torch.Tensor,
+                  kn: torch.Tensor, vc: torch.Tensor, beta: torch.Tensor, decay: torch.Tensor, ctx,
+                  n_heads: int, n_kv: int, key_dim: int, value_dim: int, taps: int) -> None:
+    """First step of the gated delta rule (csrc/recurrent.cu): from projected rows
+    ``[q | k | v | gate | b | a]`` the convolved, activated and unit-length q and k, the
+    convolved v, beta and the decay, all 32-bit; then the convolution history of every
+    sequence is brought up to the step's end.  ``state``: ``[slots, floats]``, the history
+    ``[taps - 1, channels]`` begins at ``hist_offset``."""
+    rows = proj.shape[0]
+    _want(proj, proj.dtype, "proj")
+    _want(state, torch.float32, "state")
+    nqk, nv = n_kv * key_dim, n_heads * value_dim
+    if proj.shape[1] != 2 * nqk + 2 * nv + 2 * n_heads:
+        raise KernelError("delta_prepare: a projected row must hold q, k, v, gate, b and a")
+    _f32(conv_w, (2 * nqk + nv) * taps, "conv_w")
+    _f32(a_log, n_heads, "a_log")
+    _f32(dt_bias, n_heads, "dt_bias")
+    for t, n, nm in ((qn, rows * nqk, "qn"), (kn, rows * nqk, "kn"), (vc, rows * nv, "vc"),
+                     (beta, rows * n_heads, "beta"), (decay, rows * n_heads, "decay")):
+        _f32(t, n, nm)
+    if state.shape[1] < hist_offset + (taps - 1) * (2 * nqk + nv):
+        raise KernelError("delta_prepare: the state is too small for the history")
+    _check(library().sib_delta_prepare(
+        _ptr(proj), c_longlong(proj.stride(0)), _code(proj.dtype), _ptr(conv_w), _ptr(a_log),
+        _ptr(dt_bias), _ptr(state), c_longlong(state.stride(0)), c_longlong(hist_offset), _ptr(qn),
+        _ptr(kn), _ptr(vc), _ptr(beta), _ptr(decay), _ptr(ctx.row_pos), _ptr(ctx.row_seq),
+        _ptr(ctx.seq_slot), _ptr(ctx.seq_start), _ptr(ctx.seq_end), _ptr(ctx.seq_row0), c_int(rows),
+        c_int(ctx.n_seqs), c_int(n_heads), c_int(n_kv), c_int(key_dim), c_int(value_dim),
+        c_int(taps), _stream()))
+
+
+def _scan_work(kind, rows, n_seqs, n_heads, key_dim, cols):
+    state = n_seqs * n_heads * key_dim * cols * 4
+    return kind, 2 * state + rows * n_heads * (2 * key_dim + 2 * cols) * 4, \
+        6.0 * rows * n_heads * key_dim * cols
+
+
+@_timed(lambda qn, kn, vc, decay, beta, state, out, ctx, n_heads, n_kv, key_dim, value_dim: _scan_work(
+    "delta_scan", out.shape[0], ctx.n_seqs, n_heads, key_dim, value_dim))
+def delta_scan(qn: torch.Tensor, kn: torch.Tensor, vc: torch.Tensor, decay: torch.Tensor,
+               beta: torch.Tensor, state: torch.Tensor, out: torch.Tensor, ctx, n_heads: int,
+               n_kv: int, key_dim: int, value_dim: int) -> torch.Tensor:
+    """The gated delta rule over the step's rows, sequence by sequence, from and into the
+    slots' matrices ``state[slot, :heads * value_dim * key_dim]``; ``out`` 32-bit
+    ``[rows, heads * value_dim]``."""
+    rows = out.shape[0]
+    _want(state, torch.float32, "state")
+    _f32(out, rows * n_heads * value_dim, "out")
+    if state.shape[1] < n_heads * value_dim * key_dim:
+        raise KernelError("delta_scan: the state is too small for the matrices")
+    _check(library().sib_delta_scan(
+        _ptr(qn), _ptr(kn), _ptr(vc), _ptr(decay), _ptr(beta), _ptr(state),
+        c_longlong(state.stride(0)), _ptr(out), _ptr(ctx.seq_slot), _ptr(ctx.seq_start),
+        _ptr(ctx.seq_end), _ptr(ctx.seq_row0), c_int(rows), c_int(ctx.n_seqs), c_int(n_heads),
+        c_int(n_kv), c_int(key_dim), c_int(value_dim), _stream()))
+    return out
+
+
+@_timed(lambda proj, bias_i, bias_f, cap, state, out, m_out, ctx, n_heads, key_dim, value_dim: _scan_work(
+    "memory_scan", out.shape[0], ctx.n_seqs, n_heads, key_dim, value_dim + 1))
+def memory_scan(proj: torch.Tensor, bias_i: torch.Tensor, bias_f: torch.Tensor, cap: float,
+                state: torch.Tensor, out: torch.Tensor, m_out: torch.Tensor, ctx, n_heads: int,
+                key_dim: int, value_dim: int) -> torch.Tensor:
+    """The matrix memory with exponential gates over the step's rows.  ``proj``:
+    ``[q | k | v | gate | i | f]`` per row; ``out`` 32-bit ``[rows, heads * (value_dim + 1)]``
+    (the last column of a head is <n, q>), ``m_out`` ``[rows, heads]`` the running maxima;
+    ``state[slot]``: the matrices with n as one more column, then the maxima."""
+    rows = proj.shape[0]
+    _want(proj, proj.dtype, "proj")
+    _want(state, torch.float32, "state")
+    nq, nv = n_heads * key_dim, n_heads * value_dim
+    if proj.shape[1] != 2 * nq + 2 * nv + 2 * n_heads:
+        raise KernelError("memory_scan: a projected row must hold q, k, v, gate, i and f")
+    _f32(bias_i, n_heads, "bias_i")
+    _f32(bias_f, n_heads, "bias_f")
+    _f32(out, rows * n_heads * (value_dim + 1), "out")
+    _f32(m_out, rows * n_heads, "m_out")
+    if state.shape[1] < n_heads * (value_dim + 1) * key_dim + n_heads:
+        raise KernelError("memory_scan: the state is too small")
+    _check(library().sib_memory_scan(
+        _ptr(proj), c_longlong(proj.stride(0)), _code(proj.dtype), c_longlong(2 * nq + 2 * nv),
+        c_longlong(2 * nq + 2 * nv + n_heads), _ptr(bias_i), _ptr(bias_f), c_float(cap), _ptr(state),
+        c_longlong(state.stride(0)), _ptr(out), _ptr(m_out), _ptr(ctx.seq_slot), _ptr(ctx.seq_start),
+        _ptr(ctx.seq_end), _ptr(ctx.seq_row0), c_int(rows), c_int(ctx.n_seqs), c_int(n_heads),
+        c_int(key_dim), c_int(value_dim), _stream()))
+    return out
+
+
+@_timed(lambda o, m, w, gate, y, *a: ("head_norm_gate", _nbytes(o, y) + _nbytes(y), 0))
+def head_norm_gate(o: torch.Tensor, m: Optional[torch.Tensor], w: torch.Tensor,
+                   gate: torch.Tensor, y: torch.Tensor, n_heads: int, value_dim: int, eps: float,
+                   act: int) -> torch.Tensor:
+    """y[r, h, :] = x / rms(x) * w * act(gate[r, h, :]) with x the head's 32-bit output
+    (``o`` ``[rows, heads * cols]``, the first ``value_dim`` columns of a head; with ``m``
+    divided by max(|column value_dim|, e^-m) + 1e-6 first).  ``w``: one weight per column
+    shared by the heads, or one per head and column.  ``gate``: a view ``[rows, heads *
+    value_dim]``.  act: GATE_SILU or GATE_SIGMOID."""
+    rows = y.shape[0]
+    _want(o, torch.float32, "o")
+    _want(y, y.dtype, "y")
+    _want(w, torch.float32, "w")
+    _want(gate, y.dtype, "gate", contiguous=False)
+    cols = o.shape[1] // n_heads
+    if tuple(y.shape) != (rows, n_heads * value_dim) or o.shape[0] != rows or cols < value_dim:
+        raise KernelError("head_norm_gate: shapes do not fit the head counts")
+    if w.numel() not in (value_dim, n_heads * value_dim):
+        raise KernelError("head_norm_gate: the weight is per column or per head and column")
+    if tuple(gate.shape) != (rows, n_heads * value_dim) or gate.stride(1) != 1:
+        raise KernelError("head_norm_gate: one gate value per output")
+    if m is not None:
+        _f32(m, rows * n_heads, "m")
+    _check(library().sib_head_norm_gate(
+        _ptr(o), _ptr(m), _ptr(w), c_int(0 if w.numel() == value_dim else value_dim), _ptr(gate),
+        c_longlong(gate.stride(0)), _ptr(y), _code(y.dtype), c_int(rows), c_int(n_heads),
+        c_int(value_dim), c_int(cols), c_float(eps), c_int(act), _stream()))
+    return y
 
 
 def attention_rows_scratch_bytes(rows: int, n_heads: int, head_dim: int, splits: int) -> int:

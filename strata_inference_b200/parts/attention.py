@@ -24,6 +24,24 @@ rotate-and-store kernel); prompts take the tcgen05 attention for head sizes
 64/128/256 with at most two query heads per kv head, else the mma.sync
 kernel, else the general one; single rows over the cache take the
 bandwidth-tuned kernel for head sizes 64/128/256 and groups of 1, 2, 4 or 8.
+
+Optional, each off unless its parameter is given (csrc/head_prepare.cu does them between
+the projection and the attention kernel, in 32-bit):
+
+``value_dim``   width of a value head where it differs from ``head_dim``.  The packed
+                rows and the cache then hold heads of max(head_dim, value_dim) rounded up
+                to 16, the narrower kind filled up with zeros, so every attention kernel
+                serves them; the output is narrowed again before the output product.
+``bias``        q, k and v have biases (``q_proj.bias`` ...).
+``qk_norm``     {"eps": e}: q and k are divided by their root mean square per head and
+                multiplied by ``q_norm.weight`` / ``k_norm.weight`` (one per dimension,
+                shared by the heads), before the rotation.
+``value_mix``   "first": this layer's values are also what later layers mix in;
+                "mix": v <- (1 - l) v + l v_first with l = ``value_mix.weight`` (one number)
+                and v_first the "first" layer's values of the same token; the mixed values
+                are the ones cached.
+``head_gate``   each head's output is multiplied by sigmoid(g_h), g = ``g_proj.weight`` x
+                (one number per head, from the mixer's input), before the output product.
 """
 
 from __future__ import annotations
@@ -89,14 +107,35 @@ class Attention:
         return hasattr(self.position, "rotary") or getattr(self.position, "captures_prompts", False)
 
     @staticmethod
+    def _extras(params: Mapping) -> bool:
+        """Whether the heads are worked on between the projection and the attention."""
+        return bool(params.get("bias") or params.get("qk_norm") or params.get("value_mix")
+                    or params.get("head_gate")
+                    or int(params.get("value_dim") or params["head_dim"]) != params["head_dim"])
+
+    @staticmethod
     def tensors(params: Mapping, hidden: int) -> Dict[str, TensorDecl]:
         nh, nkv, hd = params["num_heads"], params["num_kv_heads"], params["head_dim"]
+        vd = int(params.get("value_dim") or hd)
         out = {
             "q_proj.weight": TensorDecl((nh * hd, hidden)),
             "k_proj.weight": TensorDecl((nkv * hd, hidden)),
-            "v_proj.weight": TensorDecl((nkv * hd, hidden)),
-            "o_proj.weight": TensorDecl((hidden, nh * hd)),
+            "v_proj.weight": TensorDecl((nkv * vd, hidden)),
+            "o_proj.weight": TensorDecl((hidden, nh * vd)),
         }
+        if params.get("bias"):
+            out["q_proj.bias"] = TensorDecl((nh * hd,), init="norm")
+            out["k_proj.bias"] = TensorDecl((nkv * hd,), init="norm")
+            out["v_proj.bias"] = TensorDecl((nkv * vd,), init="norm")
+        if params.get("qk_norm"):
+            out["q_norm.weight"] = TensorDecl((hd,), init="norm")
+            out["k_norm.weight"] = TensorDecl((hd,), init="norm")
+        if params.get("value_mix"):
+            # (the layer whose values the others mix in may store a weight too; it is not read)
+            out["value_mix.weight"] = TensorDecl((), init="norm",
+                                                 optional=params["value_mix"] == "first")
+        if params.get("head_gate"):
+            out["g_proj.weight"] = TensorDecl((nh, hidden))
         pos: PartSpec = params["position"]
         for name, decl in part_class("position", pos.kind).tensors(pos.params, hd).items():
             out["position." + name] = decl
@@ -106,12 +145,26 @@ class Attention:
     def resident(params: Mapping, hidden: int) -> Dict[str, Resident]:
         """q, k and v are kept as ONE matrix (one product makes all three)."""
         nh, nkv, hd = params["num_heads"], params["num_kv_heads"], params["head_dim"]
+        vd = int(params.get("value_dim") or hd)
+        n_qkv = (nh + nkv) * hd + nkv * vd
+        pieces = (Piece("q_proj.weight", 0), Piece("k_proj.weight", nh * hd),
+                  Piece("v_proj.weight", (nh + nkv) * hd))
+        if params.get("head_gate"):       # the gates' rows behind q, k and v: one product makes all
+            pieces += (Piece("g_proj.weight", n_qkv),)
         out = {
-            "qkv_proj.weight": Resident(((nh + 2 * nkv) * hd, hidden), pieces=(
-                Piece("q_proj.weight", 0), Piece("k_proj.weight", nh * hd),
-                Piece("v_proj.weight", (nh + nkv) * hd))),
-            "o_proj.weight": Resident((hidden, nh * hd), pieces=(Piece("o_proj.weight"),)),
+            "qkv_proj.weight": Resident((n_qkv + (nh if params.get("head_gate") else 0), hidden),
+                                        pieces=pieces),
+            "o_proj.weight": Resident((hidden, nh * vd), pieces=(Piece("o_proj.weight"),)),
         }
+        if params.get("bias"):
+            out["qkv_proj.bias"] = Resident((n_qkv,), torch.float32, (
+                Piece("q_proj.bias", 0), Piece("k_proj.bias", nh * hd),
+                Piece("v_proj.bias", (nh + nkv) * hd)))
+        if params.get("qk_norm"):
+            out["q_norm.gain"] = Resident((hd,), torch.float32, (Piece("q_norm.weight"),))
+            out["k_norm.gain"] = Resident((hd,), torch.float32, (Piece("k_norm.weight"),))
+        if params.get("value_mix") == "mix":
+            out["value_mix.weight"] = Resident((1,), torch.float32, (Piece("value_mix.weight"),))
         pos: PartSpec = params["position"]
         cls = part_class("position", pos.kind)
         for name, res in resident_of(cls, cls.tensors(pos.params, hd), pos.params, hd).items():
@@ -131,12 +184,33 @@ class Attention:
         self.window = int(params.get("window") or 0)
         if self.nh <= 0 or self.nkv <= 0 or self.nh % self.nkv:
             raise ConfigError(f"attention: {self.nh} heads cannot share {self.nkv} kv heads")
-        if self.hd % 16 or not 16 <= self.hd <= 512:
+        self.vd = int(params.get("value_dim") or self.hd)
+        self.extras = self._extras(params)
+        # kw: how wide a head is in the packed rows, in the cache and for the attention kernels
+        self.kw = -(-max(self.hd, self.vd) // 16) * 16 if self.extras else self.hd
+        if self.kw % 16 or not 16 <= self.kw <= 512 or self.hd <= 0 or self.vd <= 0:
             raise ConfigError(f"attention: head_dim {self.hd} must be a multiple of 16 "
-                              f"between 16 and 512")
+                              f"between 16 and 512 (any size up to 512 with worked-on heads)")
         pos: PartSpec = params["position"]
         pos_w = {k[len("position."):]: v for k, v in weights.items() if k.startswith("position.")}
         self.position = part_class("position", pos.kind)(pos.params, self.hd, pos_w, rt)
+        if self.extras:
+            if self.window:
+                raise ConfigError("attention: a window together with worked-on heads is not built")
+            norm = params.get("qk_norm")
+            self.qk_eps = float(norm["eps"]) if norm else 0.0
+            self.bias = weights.get("qkv_proj.bias")
+            self.q_gain, self.k_gain = weights.get("q_norm.gain"), weights.get("k_norm.gain")
+            self.value_mix = params.get("value_mix") or None
+            if self.value_mix not in (None, "first", "mix"):
+                raise ConfigError(f"attention: value_mix {self.value_mix!r} is not 'first' or 'mix'")
+            self.lam = weights.get("value_mix.weight")
+            self.head_gate = bool(params.get("head_gate"))
+            self.n_qkv = (self.nh + self.nkv) * self.hd + self.nkv * self.vd
+            rotary = self.position.rotary() if hasattr(self.position, "rotary") else None
+            if rotary is None or rotary[2] != native.ROPE_HALF_SPLIT:
+                raise ConfigError("attention: worked-on heads take a rotary position part with "
+                                  "half-split pairs (or 'none')")
         self.w_qkv = rt.cast_matrix(weights["qkv_proj.weight"])
         self.w_q = self.w_qkv[: self.nh * self.hd]
         self.w_o = rt.cast_matrix(weights["o_proj.weight"])
@@ -145,7 +219,7 @@ class Attention:
         self._block_warps = tuple(int(w) for w in os.environ.get("SIB_DECODE_WARPS", "8,4,2").split(","))
 
     def cache_need(self) -> Optional[CacheNeed]:
-        return CacheNeed(kv=KVNeed(self.nkv, self.hd, self.window))
+        return CacheNeed(kv=KVNeed(self.nkv, self.kw, self.window))
 
     # ------------------------------------------------------------------
     def _longest(self, ctx, capacity: int) -> int:
@@ -174,7 +248,7 @@ class Attention:
         Gemma2-2B shape, context 8 192: batch 1 1.83 -> 1.74 ms, batch 2 1.95 -> 1.84, batch 4
         2.06 -> 2.04; batch 6 and 8 are better off with blocks of 4)."""
         if self._resident_warps is None:     # what the device holds of this kernel at a time
-            self._resident_warps = {w: native.attention_decode_resident_warps(self.nh, self.nkv, self.hd, w)
+            self._resident_warps = {w: native.attention_decode_resident_warps(self.nh, self.nkv, self.kw, w)
                                     for w in (8, 4)}
         return decode_shape(max(1, ctx.n_rows * self.nkv), self._longest(ctx, capacity), self.window,
                             self._resident_warps[4], self._resident_warps[8], self._block_warps)
@@ -195,7 +269,7 @@ class Attention:
         prompt kernel runs over it with the rows before each piece as keys only.  (Row by row
         over the cache, as single-token steps do it, every row reads its sequence's whole
         past: 4 096 tokens in pieces of 512 took 183 ms instead of 15 ms in one piece.)"""
-        rt, nh, nkv, hd = self.rt, self.nh, self.nkv, self.hd
+        rt, nh, nkv, hd = self.rt, self.nh, self.nkv, self.kw
         memo = ctx.memo.setdefault(("pieces", self.window), {})
         if not memo:
             starts, counts = ctx.starts, ctx.counts
@@ -243,10 +317,12 @@ class Attention:
 
     def forward(self, x: torch.Tensor, ctx, entry: int, cache_entry: int,
                 owns_cache: bool) -> torch.Tensor:
-        rt, nh, hd = self.rt, self.nh, self.hd
+        rt, nh, hd = self.rt, self.nh, self.kw
         R = x.shape[0]
         nkv = self.nkv if owns_cache else 0
         view = ctx.kv(cache_entry)
+        if self.extras and not owns_cache:
+            raise ValueError("attention: worked-on heads cannot read another run's cache")
         fresh = ctx.all_from_start and owns_cache
         if not fresh and view.ring_tokens > 0 and not ctx.graph_capture:
             # rows that attend over a ring must not overwrite a key that an earlier row of
@@ -261,7 +337,25 @@ class Attention:
 
         w_in = self.w_qkv if owns_cache else self.w_q
         rotary = self.position.rotary() if hasattr(self.position, "rotary") else None
-        if (rotary is not None and rotary[1] == hd and rotary[2] == native.ROPE_HALF_SPLIT
+        proj = None
+        if self.extras:
+            # bias, norms of q and k, rotation, mixing of values and the cache write in one
+            # kernel, from the projected row to packed heads of `kw`
+            proj = rt.linear(x, w_in)
+            qkv = torch.empty((R, (nh + 2 * nkv) * hd), dtype=proj.dtype, device=proj.device)
+            v_first = None
+            if self.value_mix == "mix":
+                v_first = ctx.memo.get("value_mix.first")
+                if v_first is None:
+                    raise ValueError("attention: values to mix in, but no earlier layer left any")
+            native.head_prepare(proj, qkv, self.bias, self.q_gain, self.k_gain, self.qk_eps,
+                                rotary[0], rotary[1], v_first, self.lam if v_first is not None else None,
+                                ctx.row_pos, ctx.row_seq, ctx.seq_slot, ctx.seq_end, view.k, view.v,
+                                view.page_table, view.page_tokens, view.ring_tokens, nh, nkv,
+                                self.hd, self.vd, hd)
+            if self.value_mix == "first":
+                ctx.memo["value_mix.first"] = qkv[:, (nh + nkv) * hd:]
+        elif (rotary is not None and rotary[1] == hd and rotary[2] == native.ROPE_HALF_SPLIT
                 and x.dtype == torch.bfloat16 and rt.fuse_rotation and 0 < R <= rt.fused_rope_max_rows
                 and self.hidden % 8 == 0 and x.stride(1) == 1 and x.stride(0) % 8 == 0
                 and x.data_ptr() % 16 == 0):
@@ -354,6 +448,10 @@ class Attention:
                                   view.page_tokens, view.ring_tokens, ctx.row_pos, ctx.row_seq,
                                   ctx.seq_slot, ctx.seq_start, ctx.seq_row0, out, scratch, nh,
                                   self.nkv, hd, self.scale, self.softcap, self.window, splits)
+        if self.extras:
+            y = torch.empty((R, nh * self.vd), dtype=out.dtype, device=out.device)
+            gate = proj[:, self.n_qkv:self.n_qkv + nh] if self.head_gate else None
+            out = native.head_gate(out, gate, y, nh, self.vd, hd)
         return rt.linear(out, self.w_o)
 
 

@@ -7,7 +7,10 @@ before the add, as in src/model/layer.rs:1101-1192):
     h += post_mixer(mixer(pre_mixer(h)))
     h += post_feed_forward(feed_forward(pre_feed_forward(h)))
 
-``pre_norm`` is the same arrangement without the two post norms.  The
+``pre_norm`` is the same arrangement without the two post norms.  A layer without a
+feed-forward (``feed_forward`` None) has the first line only.  A site whose norm is the
+``identity`` norm passes the stream's rows on as they are, which gives the arrangement
+that norms a sub-layer's output only: h += post(sublayer(h)).  The
 residual stream h is kept and summed in 32-bit.  When the norms around an
 add are RMS norms the block runs "norm of the sub-layer's output, add, norm
 for the next sub-layer" as one kernel (csrc/norm.cu add_rms_norm), reaching
@@ -34,13 +37,13 @@ class SandwichBlock:
 
     def __init__(self, mixer, feed_forward, norms: Mapping[str, object], rt):
         for site in self.required_sites:
-            if norms.get(site) is None:
+            if norms.get(site) is None and (feed_forward is not None or site == "pre_mixer"):
                 raise ConfigError(f"block: the '{site}' norm is required")
         self.mixer = mixer
-        self.feed_forward = feed_forward
+        self.feed_forward = feed_forward       # None: the layer is its mixer alone
         self.pre_mixer = norms["pre_mixer"]
         self.post_mixer = norms.get("post_mixer")
-        self.pre_ff = norms["pre_feed_forward"]
+        self.pre_ff = norms.get("pre_feed_forward")
         self.post_ff = norms.get("post_feed_forward")
         self.rt = rt
 
@@ -54,10 +57,10 @@ class SandwichBlock:
         (parts/base.py Runtime.chaining): its mixer and feed-forward promise to touch
         deferred results through the runtime and ``kernels.native`` only, and its norms are
         the kind the residual kernel applies."""
+        norms = (self.pre_mixer, self.post_mixer, self.pre_ff, self.post_ff)
         return (getattr(self.mixer, "chain_safe", False)
                 and getattr(self.feed_forward, "chain_safe", False)
-                and all(_fusable(n) for n in (self.pre_mixer, self.post_mixer, self.pre_ff,
-                                              self.post_ff)))
+                and all(_fusable(n) and (n is None or n.gain is not None) for n in norms))
 
     @property
     def captures_prompts(self) -> bool:
@@ -65,7 +68,8 @@ class SandwichBlock:
         its mixer and feed-forward promise to read sequences, slots and counts on the
         device only (the block itself and the norms work row by row)."""
         return (getattr(self.mixer, "captures_prompts", False)
-                and getattr(self.feed_forward, "captures_prompts", False))
+                and (self.feed_forward is None
+                     or getattr(self.feed_forward, "captures_prompts", False)))
 
     def _add_then_norm(self, y: torch.Tensor, post, h: torch.Tensor, nxt) -> Optional[torch.Tensor]:
         """h += post(y) (or y); returns nxt(h) if nxt is given."""
@@ -88,6 +92,8 @@ class SandwichBlock:
             self.rt.flush()
             normed = self.pre_mixer.forward(h, out_dtype=self.rt.dtype)
         a = self.mixer.forward(normed, ctx, entry, cache_entry, owns_cache)
+        if self.feed_forward is None:
+            return self._add_then_norm(a, self.post_mixer, h, next_norm)
         n2 = self._add_then_norm(a, self.post_mixer, h, self.pre_ff)
         f = self.feed_forward.forward(n2, ctx)
         return self._add_then_norm(f, self.post_ff, h, next_norm)

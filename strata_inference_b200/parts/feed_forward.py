@@ -1,4 +1,5 @@
-"""The dense gated feed-forward: down(act(gate(x)) * up(x)), no biases.
+"""The dense gated feed-forward: down(act(gate(x)) * up(x)), no biases; act is the
+tanh-GELU or SiLU (``activation``: "gelu_pytorch_tanh", "silu").
 
 Reference: src/model/layer.rs:696-710 (two products, the gated activation,
 the down product), src/backend/cpu.rs:1190-1199 (tanh-GELU).  The gate and up
@@ -21,7 +22,9 @@ from ..weights.arena import Piece, Resident
 from ..weights.loader import TensorDecl
 from .registry import register_feed_forward
 
-_ACTIVATIONS = ("gelu_pytorch_tanh",)
+# activation of the gate -> (elementwise kernel's code, fused epilogue of the products or None)
+_ACTIVATIONS = {"gelu_pytorch_tanh": (native.ACT_GELU_TANH, native.EPI_GEGLU),
+                "silu": (native.ACT_SILU, None)}
 _GROUP = 8
 
 
@@ -56,10 +59,11 @@ class GatedMLP:
     def __init__(self, params: Mapping, hidden: int, weights: Mapping[str, torch.Tensor], rt):
         self.rt = rt
         self.inter = int(params["intermediate_size"])
-        act = params.get("activation", _ACTIVATIONS[0])
+        act = params.get("activation", "gelu_pytorch_tanh")
         if act not in _ACTIVATIONS:
             raise ConfigError(f"gated_mlp: activation {act!r} is not supported; "
                               f"known: {', '.join(_ACTIVATIONS)}")
+        self.act, self.epilogue = _ACTIVATIONS[act]
         self.group = _GROUP if self.inter % _GROUP == 0 else 0
         self.w_gate_up = rt.cast_matrix(weights["gate_up_proj.weight"])
         self.w_down = rt.cast_matrix(weights["down_proj.weight"])
@@ -67,14 +71,15 @@ class GatedMLP:
     def forward(self, x: torch.Tensor, ctx) -> torch.Tensor:
         rt = self.rt
         R = x.shape[0]
-        if (self.group == _GROUP and x.dtype == torch.bfloat16 and x.shape[1] % 8 == 0
+        if (self.epilogue is not None and self.group == _GROUP and x.dtype == torch.bfloat16
+                and x.shape[1] % 8 == 0
                 and (R <= rt.skinny_max_rows or R > rt.gated_gemm_min_rows
                      or (rt.chain is not None and R <= rt.chain_max_rows))):
-            t = rt.linear(x, self.w_gate_up, epilogue=native.EPI_GEGLU)
+            t = rt.linear(x, self.w_gate_up, epilogue=self.epilogue)
         else:
             gate_up = rt.linear(x, self.w_gate_up)
             t = torch.empty((R, self.inter), dtype=x.dtype, device=x.device)
-            native.gelu_mul(gate_up, t, self.group)
+            native.gelu_mul(gate_up, t, self.group, self.act)
         return rt.linear(t, self.w_down)
 
 

@@ -5,6 +5,11 @@ that store the weight as a deviation from one) instead of gain = weight
 (the reference's convention, src/backend/cpu.rs:797-810, whose input files
 already hold the effective gain).  The gain is formed once, in 32-bit, when
 the weights are placed on the device.
+
+``identity`` is the norm of a site that has none: the rows of the 32-bit stream as
+activations, unchanged.  A layer whose sub-layers read the stream itself and are normed
+on the way out only (x <- x + norm(sublayer(x))) names it at its two "pre" sites, so
+that the block arrangements and their fused "norm, add, norm" step serve it as they are.
 """
 
 from __future__ import annotations
@@ -44,4 +49,33 @@ class RMSNorm:
         return native.rms_norm(x, self.gain, self.eps, out, rows)
 
 
+class IdentityNorm:
+    """No norm: rows pass as they are (in the activation type).  ``gain`` None with
+    ``fusable_rms`` tells a block that the residual kernel writes the plain rows out."""
+
+    fusable_rms = True
+    gain = None
+    eps = 0.0
+
+    @staticmethod
+    def tensors(params: Mapping, hidden: int) -> Dict[str, TensorDecl]:
+        return {}
+
+    @staticmethod
+    def resident(params: Mapping, hidden: int) -> Dict[str, Resident]:
+        return {}
+
+    def __init__(self, params: Mapping, hidden: int, weights: Mapping[str, torch.Tensor], rt):
+        self.hidden = hidden
+        self.rt = rt
+
+    def forward(self, x: torch.Tensor, out_dtype: Optional[torch.dtype] = None,
+                rows: Optional[torch.Tensor] = None) -> torch.Tensor:
+        if rows is not None:
+            raise ValueError("the identity norm takes whole steps, not chosen rows")
+        out = torch.empty((x.shape[0], self.hidden), dtype=out_dtype or self.rt.dtype, device=x.device)
+        return native.cast_rows(x, out)
+
+
 register_norm("rms_norm", RMSNorm)
+register_norm("identity", IdentityNorm)

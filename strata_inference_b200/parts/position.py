@@ -5,6 +5,7 @@
 reference: freq_i = theta^((-1/rot) * 2i) evaluated in 32-bit
 (src/backend/cpu.rs:1276-1282); the angle pos * freq_i and its sine and
 cosine are taken in 32-bit inside the kernel (csrc/rope_cache.cu).
+``scaling_factor`` (default 1) divides every frequency: positions stretched linearly.
 ``none``: no encoding.
 
 A position part offers ``rotary()`` -> (inv_freq, rotary_dim, style) for the
@@ -41,6 +42,11 @@ class Rope:
         inv_ndims = torch.tensor(-1.0 / self.rotary_dim, dtype=torch.float32)
         two_i = torch.arange(self.rotary_dim // 2, dtype=torch.float32) * 2.0
         freqs = torch.pow(torch.tensor(self.theta, dtype=torch.float32), inv_ndims * two_i)
+        self.scaling_factor = float(params.get("scaling_factor") or 1.0)
+        if self.scaling_factor <= 0:
+            raise ConfigError(f"scaling_factor {self.scaling_factor} must be positive")
+        if self.scaling_factor != 1.0:
+            freqs = freqs / self.scaling_factor
         self.inv_freq = freqs.to(rt.device).contiguous()
 
     def rotary(self) -> Tuple[Optional[torch.Tensor], int, int]:

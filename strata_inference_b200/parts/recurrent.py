@@ -1,0 +1,214 @@
+"""Mixers that carry a matrix per head from token to token instead of keys and values.
+
+Both keep their state in the cache's per-slot state (``StateNeed``, 32-bit, zeroed when a
+slot is taken), read and write it by the step's device tensors only (so their steps can be
+recorded and replayed) and take any split of a sequence into steps: a step continues from
+what the slot holds.  One product makes every projection of the mixer's input; what enters
+the recurrence besides the projections (unit norms, decays, gates, the state) is 32-bit
+(csrc/recurrent.cu).
+
+``gated_delta``  the gated delta rule.  Parameters: ``num_heads`` H (value heads),
+    ``num_kv_heads`` G (q and k heads; value head h reads q/k head h // (H / G)),
+    ``head_dim`` (q, k), ``value_dim``, ``conv_taps``, ``norm_eps``.
+    q, k, v pass a causal convolution over the last ``conv_taps`` tokens per channel (no
+    bias, zeros before the start) and SiLU; q and k become unit vectors per head
+    (x / sqrt(sum x^2 + 1e-6)), q times head_dim^-1/2; beta = sigmoid(b_proj x);
+    decay = exp(-exp(A_log) * softplus(a_proj x + dt_bias)); per head
+        S <- decay S;  u = beta (v - S^T k);  S <- S + k u^T;  o = S^T q
+    then o / rms(o) * norm.weight (one per value dimension) * silu(g_proj x), and o_proj.
+    State: the matrices and the convolutions' last ``conv_taps - 1`` inputs.
+
+``matrix_memory``  the matrix memory with exponential gates (mLSTM).  Parameters:
+    ``num_heads``, ``head_dim``, ``value_dim``, ``gate_cap`` c, ``norm_eps``.
+    i = c tanh((i_proj x + bias) / c);  f = log sigmoid(c tanh((f_proj x + bias) / c));
+        m' = max(f + m, i);  S <- e^(f + m - m') S + e^(i - m') k v^T;  n likewise with k
+        o = S^T q / (max(|n . q|, e^-m') + 1e-6),      q = q_proj x * head_dim^-1/2
+    then per head o / rms(o), times norm.weight (one per head and dimension) and
+    sigmoid(g_proj x), and o_proj.  State: S, n and m (m starts at 0).
+"""
+
+from __future__ import annotations
+
+from typing import Dict, Mapping, Optional
+
+import torch
+
+from ..cache.paged import CacheNeed, StateNeed
+from ..config.spec import ConfigError
+from ..kernels import native
+from ..weights.arena import Piece, Resident
+from ..weights.loader import TensorDecl
+from .registry import register_mixer
+
+
+def _pieces(rows):
+    """Pieces stacked in the given order: [(stored name, rows)] -> (pieces, total rows)."""
+    out, at = [], 0
+    for name, n in rows:
+        out.append(Piece(name, at))
+        at += n
+    return tuple(out), at
+
+
+class GatedDeltaRule:
+    captures_prompts = True      # sequences, slots and counts are read on the device only
+
+    @staticmethod
+    def _sizes(params: Mapping):
+        H, G = int(params["num_heads"]), int(params["num_kv_heads"])
+        kd, vd, taps = int(params["head_dim"]), int(params["value_dim"]), int(params["conv_taps"])
+        if H <= 0 or G <= 0 or H % G:
+            raise ConfigError(f"gated_delta: {H} heads cannot share {G} q/k heads")
+        if not 0 < kd <= 256 or vd <= 0 or not 1 <= taps <= 64:
+            raise ConfigError(f"gated_delta: head_dim {kd} (at most 256), value_dim {vd}, "
+                              f"{taps} taps (1 to 64)")
+        return H, G, kd, vd, taps
+
+    @classmethod
+    def _in_rows(cls, params: Mapping):
+        H, G, kd, vd, _ = cls._sizes(params)
+        return [("q_proj.weight", G * kd), ("k_proj.weight", G * kd), ("v_proj.weight", H * vd),
+                ("g_proj.weight", H * vd), ("b_proj.weight", H), ("a_proj.weight", H)]
+
+    @classmethod
+    def tensors(cls, params: Mapping, hidden: int) -> Dict[str, TensorDecl]:
+        H, G, kd, vd, taps = cls._sizes(params)
+        out = {name: TensorDecl((n, hidden)) for name, n in cls._in_rows(params)}
+        out.update({
+            "q_conv.weight": TensorDecl((G * kd, taps), init="norm"),
+            "k_conv.weight": TensorDecl((G * kd, taps), init="norm"),
+            "v_conv.weight": TensorDecl((H * vd, taps), init="norm"),
+            "A_log": TensorDecl((H,), init="norm"),
+            "dt_bias": TensorDecl((H,), init="norm"),
+            "norm.weight": TensorDecl((vd,), init="norm"),
+            "o_proj.weight": TensorDecl((hidden, H * vd)),
+        })
+        return out
+
+    @classmethod
+    def resident(cls, params: Mapping, hidden: int) -> Dict[str, Resident]:
+        H, G, kd, vd, taps = cls._sizes(params)
+        pieces, n_in = _pieces(cls._in_rows(params))
+        conv, channels = _pieces([("q_conv.weight", G * kd), ("k_conv.weight", G * kd),
+                                  ("v_conv.weight", H * vd)])
+        return {
+            "in_proj.weight": Resident((n_in, hidden), pieces=pieces),
+            "conv.weight": Resident((channels, taps), torch.float32, conv),
+            "A_log": Resident((H,), torch.float32, (Piece("A_log"),)),
+            "dt_bias": Resident((H,), torch.float32, (Piece("dt_bias"),)),
+            "norm.gain": Resident((vd,), torch.float32, (Piece("norm.weight"),)),
+            "o_proj.weight": Resident((hidden, H * vd), pieces=(Piece("o_proj.weight"),)),
+        }
+
+    def __init__(self, params: Mapping, hidden: int, weights: Mapping[str, torch.Tensor], rt):
+        self.rt = rt
+        self.H, self.G, self.kd, self.vd, self.taps = self._sizes(params)
+        self.eps = float(params["norm_eps"])
+        self.channels = 2 * self.G * self.kd + self.H * self.vd
+        self.matrices = self.H * self.vd * self.kd       # floats of a slot's state before the history
+        self.w_in = rt.cast_matrix(weights["in_proj.weight"])
+        self.w_o = rt.cast_matrix(weights["o_proj.weight"])
+        self.conv_w = weights["conv.weight"]
+        self.a_log, self.dt_bias = weights["A_log"], weights["dt_bias"]
+        self.norm_gain = weights["norm.gain"]
+
+    def cache_need(self) -> Optional[CacheNeed]:
+        return CacheNeed(state=StateNeed((self.matrices + (self.taps - 1) * self.channels,)))
+
+    def forward(self, x: torch.Tensor, ctx, entry: int, cache_entry: int,
+                owns_cache: bool) -> torch.Tensor:
+        if not owns_cache:
+            raise ValueError("gated_delta: a recurrent state cannot be lent to another run")
+        rt, H, G, kd, vd = self.rt, self.H, self.G, self.kd, self.vd
+        R = x.shape[0]
+        state = ctx.state(cache_entry)
+        proj = rt.linear(x, self.w_in)
+        f32 = dict(dtype=torch.float32, device=x.device)
+        qn, kn = torch.empty((R, G * kd), **f32), torch.empty((R, G * kd), **f32)
+        vc = torch.empty((R, H * vd), **f32)
+        beta, decay = torch.empty((R, H), **f32), torch.empty((R, H), **f32)
+        native.delta_prepare(proj, self.conv_w, self.a_log, self.dt_bias, state, self.matrices,
+                             qn, kn, vc, beta, decay, ctx, H, G, kd, vd, self.taps)
+        o = torch.empty((R, H * vd), **f32)
+        native.delta_scan(qn, kn, vc, decay, beta, state, o, ctx, H, G, kd, vd)
+        y = torch.empty((R, H * vd), dtype=proj.dtype, device=x.device)
+        gate = proj[:, self.channels:self.channels + H * vd]
+        native.head_norm_gate(o, None, self.norm_gain, gate, y, H, vd, self.eps, native.GATE_SILU)
+        return rt.linear(y, self.w_o)
+
+
+class MatrixMemory:
+    captures_prompts = True      # sequences, slots and counts are read on the device only
+
+    @staticmethod
+    def _sizes(params: Mapping):
+        H, kd, vd = int(params["num_heads"]), int(params["head_dim"]), int(params["value_dim"])
+        if H <= 0 or not 0 < kd <= 256 or vd <= 0:
+            raise ConfigError(f"matrix_memory: {H} heads, head_dim {kd} (at most 256), value_dim {vd}")
+        return H, kd, vd
+
+    @classmethod
+    def _in_rows(cls, params: Mapping):
+        H, kd, vd = cls._sizes(params)
+        return [("q_proj.weight", H * kd), ("k_proj.weight", H * kd), ("v_proj.weight", H * vd),
+                ("g_proj.weight", H * vd), ("i_proj.weight", H), ("f_proj.weight", H)]
+
+    @classmethod
+    def tensors(cls, params: Mapping, hidden: int) -> Dict[str, TensorDecl]:
+        H, kd, vd = cls._sizes(params)
+        out = {name: TensorDecl((n, hidden)) for name, n in cls._in_rows(params)}
+        out.update({
+            "i_proj.bias": TensorDecl((H,), init="norm"),
+            "f_proj.bias": TensorDecl((H,), init="norm"),
+            "norm.weight": TensorDecl((H * vd,), init="norm"),
+            "o_proj.weight": TensorDecl((hidden, H * vd)),
+        })
+        return out
+
+    @classmethod
+    def resident(cls, params: Mapping, hidden: int) -> Dict[str, Resident]:
+        H, kd, vd = cls._sizes(params)
+        pieces, n_in = _pieces(cls._in_rows(params))
+        return {
+            "in_proj.weight": Resident((n_in, hidden), pieces=pieces),
+            "i_proj.bias": Resident((H,), torch.float32, (Piece("i_proj.bias"),)),
+            "f_proj.bias": Resident((H,), torch.float32, (Piece("f_proj.bias"),)),
+            "norm.gain": Resident((H * vd,), torch.float32, (Piece("norm.weight"),)),
+            "o_proj.weight": Resident((hidden, H * vd), pieces=(Piece("o_proj.weight"),)),
+        }
+
+    def __init__(self, params: Mapping, hidden: int, weights: Mapping[str, torch.Tensor], rt):
+        self.rt = rt
+        self.H, self.kd, self.vd = self._sizes(params)
+        self.eps = float(params["norm_eps"])
+        self.cap = float(params["gate_cap"])
+        if self.cap <= 0:
+            raise ConfigError(f"matrix_memory: gate_cap {self.cap} must be positive")
+        self.w_in = rt.cast_matrix(weights["in_proj.weight"])
+        self.w_o = rt.cast_matrix(weights["o_proj.weight"])
+        self.bias_i, self.bias_f = weights["i_proj.bias"], weights["f_proj.bias"]
+        self.norm_gain = weights["norm.gain"]
+
+    def cache_need(self) -> Optional[CacheNeed]:
+        # S with n as one more column, then the running maxima
+        return CacheNeed(state=StateNeed((self.H * (self.vd + 1) * self.kd + self.H,)))
+
+    def forward(self, x: torch.Tensor, ctx, entry: int, cache_entry: int,
+                owns_cache: bool) -> torch.Tensor:
+        if not owns_cache:
+            raise ValueError("matrix_memory: a recurrent state cannot be lent to another run")
+        rt, H, kd, vd = self.rt, self.H, self.kd, self.vd
+        R = x.shape[0]
+        state = ctx.state(cache_entry)
+        proj = rt.linear(x, self.w_in)
+        o = torch.empty((R, H * (vd + 1)), dtype=torch.float32, device=x.device)
+        m = torch.empty((R, H), dtype=torch.float32, device=x.device)
+        native.memory_scan(proj, self.bias_i, self.bias_f, self.cap, state, o, m, ctx, H, kd, vd)
+        y = torch.empty((R, H * vd), dtype=proj.dtype, device=x.device)
+        gate = proj[:, 2 * H * kd + H * vd:2 * H * kd + 2 * H * vd]
+        native.head_norm_gate(o, m, self.norm_gain, gate, y, H, vd, self.eps, native.GATE_SIGMOID)
+        return rt.linear(y, self.w_o)
+
+
+register_mixer("gated_delta", GatedDeltaRule)
+register_mixer("matrix_memory", MatrixMemory)
