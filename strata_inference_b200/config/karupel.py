@@ -124,6 +124,11 @@ class KarupelConfig:
                                       f"supported; known: dense")
                 ff = _positive(mlp, "ff", where + ".mlp")
             layers.append(KarupelLayer(kind, mixer, ff))
+        shapes = {(l.mixer["kv_heads"], l.mixer["vdim"]) for l in layers
+                  if l.type == "attention" and l.mixer["v_mix"]}
+        if len(shapes) > 1:
+            raise ConfigError("config.json: layers with 'v_mix' mix values of one shape, but their "
+                              f"(kv_heads, vdim) are {sorted(shapes)}")
         most = d.get("max_positions")
         return cls(vocab=vocab, width=width, eps=eps, layers=tuple(layers),
                    max_positions=_DEFAULT_POSITIONS if most is None else _positive(d, "max_positions", ""),

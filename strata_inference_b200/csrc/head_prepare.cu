@@ -24,7 +24,7 @@ struct HeadPrepareArgs {
     const float* q_gain;       // [kd] or null
     const float* k_gain;       // [kd] or null
     const float* inv_freq;     // [rot / 2] or null
-    const void* v_first;       // row r, kv head g at v_first + r * v_first_stride + g * pad; or null
+    const void* v_first;       // row r, kv head g at v_first + r * v_first_stride + g * v_first_pad; or null
     const float* lambda;       // one value on the device (with v_first)
     const int* row_pos;
     const int* row_seq;
@@ -34,7 +34,7 @@ struct HeadPrepareArgs {
     void* v_pool;
     const int* page_table;
     long long proj_stride, v_first_stride;
-    int n_heads, n_kv, kd, vd, pad, rot;
+    int n_heads, n_kv, kd, vd, pad, rot, v_first_pad;
     int max_pages, page_tokens, ring_tokens;
     float eps;
 };
@@ -87,7 +87,7 @@ __global__ void __launch_bounds__(128) head_prepare_kernel(HeadPrepareArgs p) {
     T* out = (T*)p.qkv + (size_t)r * units * p.pad + (size_t)unit * p.pad;
     if (is_v) {
         const T* first = p.v_first
-            ? (const T*)p.v_first + (size_t)r * p.v_first_stride + (size_t)(unit - p.n_heads - p.n_kv) * p.pad
+            ? (const T*)p.v_first + (size_t)r * p.v_first_stride + (size_t)(unit - p.n_heads - p.n_kv) * p.v_first_pad
             : nullptr;
         const float lam = first ? *p.lambda : 0.f;
         for (int d = lane; d < p.pad; d += 32) {
@@ -130,7 +130,7 @@ __global__ void __launch_bounds__(128) head_prepare_kernel(HeadPrepareArgs p) {
 SIB_EXPORT int sib_head_prepare(
     const void* proj, long long proj_stride, void* qkv, int dtype, const float* bias,
     const float* q_gain, const float* k_gain, float eps, const float* inv_freq, int rot,
-    const void* v_first, long long v_first_stride, const float* lambda, const int* row_pos,
+    const void* v_first, long long v_first_stride, int v_first_pad, const float* lambda, const int* row_pos,
     const int* row_seq, const int* seq_slot, const int* seq_end, void* k_pool, void* v_pool,
     const int* page_table, int max_pages, int page_tokens, int ring_tokens, int rows, int n_heads,
     int n_kv, int kd, int vd, int pad, void* stream) {
@@ -146,10 +146,11 @@ SIB_EXPORT int sib_head_prepare(
     SIB_REQUIRE(k_pool == nullptr || (v_pool && page_table && row_seq && seq_slot && seq_end &&
                                       page_tokens > 0 && max_pages > 0),
                 "head_prepare: incomplete cache description");
-    SIB_REQUIRE(v_first == nullptr || lambda != nullptr, "head_prepare: mixing values needs lambda");
+    SIB_REQUIRE(v_first == nullptr || (lambda != nullptr && v_first_pad >= vd),
+                "head_prepare: mixing values needs lambda and heads of at least %d", vd);
     HeadPrepareArgs p{proj, qkv, bias, q_gain, k_gain, rot ? inv_freq : nullptr, v_first, lambda,
                       row_pos, row_seq, seq_slot, seq_end, k_pool, v_pool, page_table, proj_stride,
-                      v_first_stride, n_heads, n_kv, kd, vd, pad, rot, max_pages, page_tokens,
+                      v_first_stride, n_heads, n_kv, kd, vd, pad, rot, v_first_pad, max_pages, page_tokens,
                       ring_tokens, eps};
     const int units = n_heads + 2 * n_kv;
     const size_t smem = (size_t)4 * pad * sizeof(float);

@@ -411,8 +411,8 @@ def head_prepare(proj: torch.Tensor, qkv: torch.Tensor, bias: Optional[torch.Ten
     """From a projected row ``[q heads | k heads | v heads | ...]`` to the packed q|k|v rows
     the attention kernels read, heads ``pad`` wide (csrc/head_prepare.cu): bias, per-head RMS
     norm of q and k with a gain, partial rotation, values mixed with ``v_first`` (a view
-    ``[rows, n_kv * pad]`` of an earlier layer's packed rows) by ``lam``, and k and v written
-    into the paged cache."""
+    ``[rows, n_kv * its own head width]`` of an earlier layer's packed rows) by ``lam``, and
+    k and v written into the paged cache."""
     rows = proj.shape[0]
     _want(proj, qkv.dtype, "proj", contiguous=False)
     _want(qkv, qkv.dtype, "qkv")
@@ -427,10 +427,12 @@ def head_prepare(proj: torch.Tensor, qkv: torch.Tensor, bias: Optional[torch.Ten
             _want(t, torch.float32, nm)
             if t.numel() != n:
                 raise KernelError(f"head_prepare: {nm} has {t.numel()} values, expected {n}")
-    v_stride = 0
+    v_stride = v_pad = 0
     if v_first is not None:
         _want(v_first, qkv.dtype, "v_first", contiguous=False)
-        if v_first.stride(1) != 1 or tuple(v_first.shape) != (rows, n_kv * pad) or lam is None:
+        v_pad = v_first.shape[1] // max(n_kv, 1)
+        if v_first.stride(1) != 1 or tuple(v_first.shape) != (rows, n_kv * v_pad) or v_pad < value_dim \
+                or lam is None:
             raise KernelError("head_prepare: v_first must be [rows, kv heads x width] with lam")
         v_stride = v_first.stride(0)
     max_pages = 0
@@ -445,7 +447,7 @@ def head_prepare(proj: torch.Tensor, qkv: torch.Tensor, bias: Optional[torch.Ten
     _check(library().sib_head_prepare(
         _ptr(proj), c_longlong(proj.stride(0)), _ptr(qkv), _code(qkv.dtype), _ptr(bias),
         _ptr(q_gain), _ptr(k_gain), c_float(eps), _ptr(inv_freq), c_int(rotary_dim if inv_freq is not None else 0),
-        _ptr(v_first), c_longlong(v_stride), _ptr(lam), _ptr(row_pos), _ptr(row_seq), _ptr(seq_slot),
+        _ptr(v_first), c_longlong(v_stride), c_int(v_pad), _ptr(lam), _ptr(row_pos), _ptr(row_seq), _ptr(seq_slot),
         _ptr(seq_end), _ptr(k_pool), _ptr(v_pool), _ptr(page_table), c_int(max_pages),
         c_int(page_tokens), c_int(ring_tokens), c_int(rows), c_int(n_heads), c_int(n_kv),
         c_int(key_dim), c_int(value_dim), c_int(pad), _stream()))

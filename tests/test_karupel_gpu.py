@@ -1,0 +1,266 @@
+"""Karupel through the engine against the plain model (tests/plain_karupel.py): each mixer
+alone, prompts against token-by-token steps, portions, unequal batches, slots and pages used
+again, sharp attention over hundreds of keys and across page borders, odd and wide sizes,
+recorded steps, greedy generation and trace replay."""
+
+from __future__ import annotations
+
+import json
+import os
+import subprocess
+import sys
+
+import pytest
+import torch
+
+import plain_karupel as plain
+from karupel_cases import (ALONE, MIXED, ODD, SHARP, WIDE, assert_close, plain_logits, prompts)
+
+pytestmark = pytest.mark.gpu
+DTYPES = ["float32", "bfloat16"]
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def make_engine(cfg, weights, dtype, **kw):
+    from strata_inference_b200.config.registry import spec_from_config
+    from strata_inference_b200.engine.engine import Engine
+    _, spec = spec_from_config(cfg)
+    kw.setdefault("max_tokens", 2048)
+    kw.setdefault("max_seq_len", 1024)
+    return Engine(spec, weights, dtype=dtype, **kw)
+
+
+def all_rows(n):
+    return list(range(n))
+
+
+def run_whole(eng, tokens):
+    s = eng.new_sequence()
+    out = eng.step([(s, tokens)], [all_rows(len(tokens))])
+    eng.end_sequence(s)
+    return out
+
+
+def run_portions(eng, tokens, sizes):
+    """The prompt cut into steps of the given sizes (the last takes the rest)."""
+    s, at, rows = eng.new_sequence(), 0, []
+    for n in list(sizes) + [len(tokens)]:
+        part = tokens[at:at + n]
+        if not part:
+            break
+        rows.append(eng.step([(s, part)], [all_rows(len(part))]))
+        at += len(part)
+    eng.end_sequence(s)
+    return torch.cat(rows)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("name", sorted(ALONE))
+def test_each_mixer_alone(name, dtype):
+    cfg = ALONE[name]
+    w = plain.random_weights(cfg, seed=11)
+    eng = make_engine(cfg, w, dtype)
+    for toks in prompts(cfg, [1, 5, 70], seed=3):
+        assert_close(run_whole(eng, toks), plain_logits(cfg, w, toks), dtype, f"{name}, {len(toks)} tokens")
+    toks = prompts(cfg, [75], seed=4)[0]
+    assert_close(run_portions(eng, toks, [3, 1, 1, 2, 60] + [1] * 8), plain_logits(cfg, w, toks), dtype,
+                 f"{name} in portions and single tokens")
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_prompt_then_long_decoding(dtype):
+    """A prompt in one step, then 150 single-token steps (over two page borders; the
+    token steps are recorded at the second and replayed from the third)."""
+    cfg = MIXED
+    w = plain.random_weights(cfg, seed=5)
+    eng = make_engine(cfg, w, dtype)
+    toks = prompts(cfg, [190], seed=6)[0]
+    ref = plain_logits(cfg, w, toks)
+    assert_close(run_portions(eng, toks, [40] + [1] * 150), ref, dtype, "prompt of 40, then token by token")
+    assert_close(run_portions(eng, toks, [1] * 30 + [160]), ref, dtype, "token by token from the first token")
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("sizes", [[2, 2, 2, 2], [64, 64], [63, 2, 63], [1, 65, 3, 33], [17, 17, 17, 17, 17]])
+def test_portions(sizes, dtype):
+    cfg = MIXED
+    w = plain.random_weights(cfg, seed=7)
+    eng = make_engine(cfg, w, dtype)
+    toks = prompts(cfg, [140], seed=8)[0]
+    assert_close(run_portions(eng, toks, sizes), plain_logits(cfg, w, toks), dtype, f"portions {sizes}")
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_unequal_batch_against_each_alone(dtype):
+    """Prompts of 1 to 130 tokens in one step, then single-token steps together; the
+    shorter requests end earlier and a new one joins the freed slots later."""
+    cfg = MIXED
+    w = plain.random_weights(cfg, seed=9)
+    eng = make_engine(cfg, w, dtype)
+    reqs = prompts(cfg, [21, 22, 100, 160, 35], seed=10)
+    first = [1, 2, 70, 130, 5]
+    refs = [plain_logits(cfg, w, t) for t in reqs]
+    live = [0, 1, 2, 3]
+    slots = {i: eng.new_sequence() for i in live}
+    out = eng.step([(slots[i], reqs[i][:first[i]]) for i in live], [all_rows(first[i]) for i in live])
+    at = 0
+    for i in live:
+        assert_close(out[at:at + first[i]], refs[i][:first[i]], dtype, f"batched prompt {i}")
+        at += first[i]
+    pos = {i: first[i] for i in live}
+    step = 0
+    while live:
+        if step == 25:                         # the latecomer starts alone, then decodes with the rest
+            slots[4] = eng.new_sequence()
+            got = eng.step([(slots[4], reqs[4][:first[4]])], [all_rows(first[4])])
+            assert_close(got, refs[4][:first[4]], dtype, "late prompt")
+            pos[4] = first[4]
+            live.append(4)
+        out = eng.step([(slots[i], [reqs[i][pos[i]]]) for i in live], [[0]] * len(live))
+        for k, i in enumerate(live):
+            assert_close(out[k:k + 1], refs[i][pos[i]:pos[i] + 1], dtype, f"request {i}, token {pos[i]}")
+            pos[i] += 1
+        for i in list(live):
+            if pos[i] == len(reqs[i]):
+                eng.end_sequence(slots[i])
+                live.remove(i)
+        step += 1
+    assert step > 25
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_slots_and_pages_used_again(dtype):
+    """A slot that is given back and taken again starts from nothing: state, history and
+    pages of the request before leave no trace; with few pages they are all used again."""
+    cfg = MIXED
+    w = plain.random_weights(cfg, seed=12)
+    eng = make_engine(cfg, w, dtype, max_tokens=256, max_seq_len=256, max_slots=2)
+    a, b, c = prompts(cfg, [100, 90, 120], seed=13)
+    ra, rb, rc = (plain_logits(cfg, w, t) for t in (a, b, c))
+    sa = eng.new_sequence()
+    assert_close(eng.step([(sa, a[:70])], [all_rows(70)]), ra[:70], dtype, "a, first part")
+    sb = eng.new_sequence()
+    assert_close(eng.step([(sb, b[:50])], [all_rows(50)]), rb[:50], dtype, "b, first part")
+    assert_close(eng.step([(sa, a[70:])], [all_rows(30)]), ra[70:], dtype, "a, second part")
+    eng.end_sequence(sa)
+    sc = eng.new_sequence()
+    assert sc == sa
+    assert_close(eng.step([(sc, c[:110])], [all_rows(110)]), rc[:110], dtype, "c in a's slot and pages")
+    out = eng.step([(sb, [b[50]]), (sc, [c[110]])], [[0], [0]])
+    assert_close(out, torch.stack([rb[50], rc[110]]), dtype, "b and c together")
+    assert_close(eng.step([(sb, b[51:])], [all_rows(39)]), rb[51:], dtype, "b, the rest")
+    eng.end_sequence(sb)
+    eng.end_sequence(sc)
+    assert_close(run_whole(eng, a), ra, dtype, "a once more")
+
+
+def test_sharp_attention_far_keys_and_page_borders():
+    """With a large scale the softmax picks a few keys among hundreds, wherever they lie: a
+    key that is lost, shifted by one or read from the wrong page changes the logits at once.
+    Prompts, portions that end at, before and behind page borders, and single tokens."""
+    cfg, dtype = SHARP, "float32"
+    w = plain.random_weights(cfg, seed=14)
+    eng = make_engine(cfg, w, dtype)
+    toks = prompts(cfg, [330], seed=15)[0]
+    ref = plain_logits(cfg, w, toks)
+    # (the weights attend far back: over the last 100 rows, the heaviest key is often 100+ back)
+    assert_close(run_whole(eng, toks), ref, dtype, "whole prompt")
+    assert_close(run_portions(eng, toks, [64, 64, 64, 64]), ref, dtype, "portions of one page")
+    assert_close(run_portions(eng, toks, [63, 2, 63, 1, 1, 62, 66]), ref, dtype, "portions around page borders")
+    assert_close(run_portions(eng, toks, [250] + [1] * 80), ref, dtype, "single tokens over two page borders")
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("name", ["odd", "wide"])
+def test_other_sizes(name, dtype):
+    cfg = {"odd": ODD, "wide": WIDE}[name]
+    w = plain.random_weights(cfg, seed=16)
+    eng = make_engine(cfg, w, dtype)
+    a, b = prompts(cfg, [150, 37], seed=17)
+    ra, rb = plain_logits(cfg, w, a), plain_logits(cfg, w, b)
+    assert_close(run_whole(eng, a), ra, dtype, f"{name}: whole prompt")
+    assert_close(run_portions(eng, a, [2, 90] + [1] * 20), ra, dtype, f"{name}: portions and tokens")
+    sa, sb = eng.new_sequence(), eng.new_sequence()
+    out = eng.step([(sa, a[:130]), (sb, b[:30])], [[0, 129], [29]])
+    assert_close(out, torch.stack([ra[0], ra[129], rb[29]]), dtype, f"{name}: two prompts")
+    for k in range(7):
+        out = eng.step([(sa, [a[130 + k]]), (sb, [b[30 + k]])], [[0], [0]])
+        assert_close(out, torch.stack([ra[130 + k], rb[30 + k]]), dtype, f"{name}: tokens {k}")
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_recorded_prompt_steps(dtype):
+    """Prompt steps of one shape: launched, recorded, then replayed for other prompts (also
+    shorter ones, filled up with rows that belong to no sequence)."""
+    cfg = MIXED
+    w = plain.random_weights(cfg, seed=18)
+    eng = make_engine(cfg, w, dtype)
+    for n, seed in ((60, 1), (64, 2), (50, 3), (33, 4), (64, 5)):
+        toks = prompts(cfg, [n], seed=seed)[0]
+        s = eng.new_sequence()
+        out = eng.step([(s, toks)], [[0, n - 1]])
+        eng.end_sequence(s)
+        ref = plain_logits(cfg, w, toks)
+        assert_close(out, torch.stack([ref[0], ref[n - 1]]), dtype, f"prompt of {n}")
+    assert any(g.graph is not None for g in eng._prompt_graphs.values())
+
+
+def write_model(path, cfg, weights):
+    from strata_inference_b200.weights.safetensors_io import write_safetensors
+    os.makedirs(path, exist_ok=True)
+    with open(os.path.join(path, "config.json"), "w") as f:
+        json.dump(cfg, f)
+    write_safetensors(os.path.join(path, "model.safetensors"),
+                      {n: t.to(torch.bfloat16) for n, t in weights.items()})
+    return path
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_greedy_generation_through_the_generation_engine(tmp_path, dtype):
+    """Unequal prompts through generate(): every chosen token is the plain model's best (or
+    within rounding of it) given the run's own history."""
+    from strata_inference_b200 import GenerationConfig, GenerationEngine, SamplingConfig
+    cfg = MIXED
+    w = plain.random_weights(cfg, seed=19)
+    model_dir = write_model(str(tmp_path / "model"), cfg, w)
+    engine = GenerationEngine.from_dir(model_dir, dtype=dtype, max_tokens=1024, ctx=256)
+    reqs = prompts(cfg, [3, 40, 75], seed=20)
+    outs = engine.generate(reqs, GenerationConfig(max_tokens=24, sampling=SamplingConfig(temperature=0.0)))
+    tol = {"float32": 1e-4, "bfloat16": 0.15}[dtype]
+    for prompt, out in zip(reqs, outs):
+        assert len(out.token_ids) == 24 and out.stop_reason == "max_tokens"
+        logits = plain_logits(cfg, w, list(prompt) + list(out.token_ids))
+        for k, tok in enumerate(out.token_ids):
+            row = logits[len(prompt) + k - 1]
+            gap = (row.max() - row[tok]).item()
+            assert gap <= tol * row.abs().max().item(), f"token {k} ({tok}) lies {gap:.3e} below the best"
+
+
+def test_trace_replay_of_a_model_folder(tmp_path):
+    cfg, dtype = ODD, "float32"
+    w = plain.random_weights(cfg, seed=21)
+    model_dir = write_model(str(tmp_path / "model"), cfg, w)
+    a, b = prompts(cfg, [80, 30], seed=22)
+    ra, rb = plain_logits(cfg, w, a), plain_logits(cfg, w, b)
+    steps = [{"step": 0, "entries": [{"id": "a", "tokens": a[:70], "want": [0, 69]},
+                                     {"id": "b", "tokens": b[:20], "want": []}], "end": []}]
+    for k in range(10):
+        steps.append({"step": k + 1, "entries": [{"id": "a", "tokens": [a[70 + k]], "want": [0]},
+                                                 {"id": "b", "tokens": [b[20 + k]], "want": [0] if k % 2 else []}],
+                      "end": ["a", "b"] if k == 9 else []})
+    out = str(tmp_path / "out")
+    p = subprocess.run([sys.executable, os.path.join(ROOT, "bin", "trace_run"), "--model", model_dir,
+                        "--dtype", dtype, "--out", out, "--max-tokens", "256"],
+                       input="\n".join(json.dumps(s) for s in steps) + "\n", capture_output=True, text=True,
+                       timeout=900)
+    assert p.returncode == 0, p.stderr[-2000:]
+    assert [l for l in p.stdout.split("\n") if l.startswith("done")] == [f"done {k}" for k in range(11)]
+    V = cfg["vocab"]
+
+    def read(step):
+        import numpy as np
+        return torch.from_numpy(np.fromfile(os.path.join(out, f"{step}.f32"), dtype="<f4").reshape(-1, V).copy())
+    assert_close(read(0), torch.stack([ra[0], ra[69]]), dtype, "prompts")
+    for k in range(10):
+        want = [ra[70 + k]] + ([rb[20 + k]] if k % 2 else [])
+        assert_close(read(k + 1), torch.stack(want), dtype, f"step {k + 1}")
