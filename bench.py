@@ -438,6 +438,105 @@ def run_sweep(args):
     return 0
 
 
+# Layer sizes for the comparison of the two architectures at equal size: (width, feed-forward,
+# heads, kv heads, head width, vocabulary, layers).  "2b" and "9b" are the Gemma2 shapes' layer
+# sizes at reduced depth; "1b" is a narrower model with heads of 128.
+KARUPEL_SIZES = {
+    "1b": (2048, 8192, 16, 8, 128, 32000, 8),
+    "2b": (2304, 9216, 8, 4, 256, 256000, 8),
+    "9b": (3584, 14336, 16, 8, 256, 256000, 8),
+}
+
+
+def karupel_config(size):
+    """Karupel at these sizes: delta, attention, matrix memory, attention, and so on, every
+    layer with a feed-forward; the recurrent mixers keep matrices of 128 x head width."""
+    width, ff, heads, kv, hd, vocab, n_layers = KARUPEL_SIZES[size]
+    mlp = {"kind": "dense", "ff": ff}
+    att = {"type": "attention", "mlp": mlp, "mixer": {
+        "heads": heads, "kv_heads": kv, "dim": hd, "vdim": hd, "scale": hd ** -0.5, "v_mix": True,
+        "rot": {"base": 10000.0, "dims": hd // 2, "scaling": {"factor": 2.0}}}}
+    dlt = {"type": "delta", "mlp": mlp, "mixer": {"heads": heads, "kv_heads": kv, "dim": 128,
+                                                    "vdim": hd, "conv": 4}}
+    mem = {"type": "mlstm", "mlp": mlp, "mixer": {"heads": heads, "dim": 128, "vdim": hd,
+                                                    "gate_cap": 15.0}}
+    pattern = [dlt, att, mem, att]
+    return {"architecture": "Karupel", "vocab": vocab, "width": width, "norm": {"eps": 1e-6},
+            "layers": [pattern[i % 4] for i in range(n_layers)]}
+
+
+def gemma2_config_like(size):
+    width, ff, heads, kv, hd, vocab, n_layers = KARUPEL_SIZES[size]
+    cfg = baseline_config()
+    cfg.update({"num_hidden_layers": n_layers, "hidden_size": width, "num_attention_heads": heads,
+                "num_key_value_heads": kv, "head_dim": hd, "intermediate_size": ff,
+                "vocab_size": vocab, "query_pre_attn_scalar": hd})
+    return cfg
+
+
+def state_bytes_per_step(engine, batch):
+    """Bytes of recurrent state a single-token step reads and writes."""
+    return sum(2 * batch * t[0].numel() * t.element_size() for t in engine.cache.state.values())
+
+
+def run_karupel(args):
+    """Karupel beside Gemma2 at equal layer sizes: a prompt step and single-token steps, and
+    (``--kernels``) the per-kernel tables of both, on standard output; one JSON line at the end."""
+    import gc
+    import torch
+    from strata_inference_b200 import GenerationEngine
+    from strata_inference_b200.engine.profile import (format_table, load_peaks,
+                                                      profile_decode_graph, profile_prompt_graph)
+    peaks = measured_peaks()
+    context, T = args.context if args.context != 8192 else 4096, 2048
+    sizes = [args.size] if args.size else sorted(KARUPEL_SIZES)
+    out = {}
+    for size in sizes:
+        for name, cfg in (("karupel", karupel_config(size)), ("gemma2", gemma2_config_like(size))):
+            batches = [1, 8, 64]
+            gen = GenerationEngine.from_random(cfg, seed=5, dtype="bfloat16", ctx=context,
+                                               max_tokens=max(batches) * context,
+                                               max_slots=max(batches))
+            engine = gen.engine
+            randomize_pools(engine)
+            weight_bytes = engine.model.weight_bytes()
+            row = {"weights_gb": round(weight_bytes / 1e9, 2)}
+            ms = time_prefill(engine, T)
+            row["prefill_2048_ms"] = round(ms, 3)
+            row["prefill_tok_s"] = round(T * 1e3 / ms, 1)
+            for b in batches:
+                dms, lengths, _, _ = time_decode(engine, b, context, max(8, args.steps // 2),
+                                                 args.warmup, 3)
+                moved = weight_bytes + kv_bytes_per_step(engine, lengths) + state_bytes_per_step(engine, b)
+                row[f"decode_b{b}_ms"] = round(dms, 4)
+                row[f"decode_b{b}_tok_s"] = round(b * 1e3 / dms, 1)
+                row[f"decode_b{b}_hbm_frac"] = round(moved / (dms * 1e-3) / 1e9 / peaks["hbm_gbs"], 3)
+            out[f"{name}_{size}"] = row
+            print(f"{name} {size}: {json.dumps(row)}", file=sys.stderr, flush=True)
+            if args.kernels:
+                pk = load_peaks()
+                slots = [engine.new_sequence() for _ in range(8)]
+                fill_context(engine, slots, context - 16)
+                rows, tms = profile_decode_graph(engine, slots, [5] * 8)
+                print(format_table(f"{name} {size}: captured decode step, batch 8, {context - 16} "
+                                   f"positions each", rows, tms, pk))
+                for s in slots:
+                    engine.end_sequence(s)
+                toks = torch.randint(0, engine.vocab_size, (T,),
+                                     generator=torch.Generator().manual_seed(4)).tolist()
+                slot = engine.new_sequence()
+                rows, tms = profile_prompt_graph(engine, slot, toks)
+                engine.end_sequence(slot)
+                print(format_table(f"{name} {size}: prompt step, {T} tokens", rows, tms, pk), flush=True)
+            del gen, engine
+            gc.collect()
+            torch.cuda.empty_cache()
+    print(json.dumps({"comparison": "Karupel beside Gemma2 at equal layer sizes (8 layers, bf16, "
+                      "random weights)", "context": context, "prompt_tokens": T,
+                      "peaks": peaks, "results": out}))
+    return 0
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -456,6 +555,11 @@ def main():
     ap.add_argument("--sweep", action="store_true",
                     help="instead of the timed run: decode steps over batch sizes at --context "
                          "and prompt steps over lengths, one line each, on standard output")
+    ap.add_argument("--karupel", action="store_true",
+                    help="instead of the timed run: Karupel beside Gemma2 at equal layer sizes "
+                         "(--size; with --kernels also the per-kernel tables of both)")
+    ap.add_argument("--size", default="", choices=[""] + sorted(KARUPEL_SIZES),
+                    help="with --karupel: one of the sizes (default: all)")
     ap.add_argument("--shape", default="2b", choices=sorted(SHAPES),
                     help="layer sizes: the 2B shape (the recorded line) or the 9B / 27B shapes")
     args = ap.parse_args()
@@ -470,6 +574,8 @@ def main():
         return 2
     if args.warmup < 3:
         args.warmup = 3
+    if args.karupel:
+        return run_karupel(args)
     if args.kernels:
         return run_kernel_tables(args)
     if args.sweep:

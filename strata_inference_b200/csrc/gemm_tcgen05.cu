@@ -23,7 +23,7 @@
 
 #include "common.cuh"
 
-enum { GEMM_EPI_NONE = 0, GEMM_EPI_SOFTCAP = 1, GEMM_EPI_GEGLU = 2 };
+enum { GEMM_EPI_NONE = 0, GEMM_EPI_SOFTCAP = 1, GEMM_EPI_GEGLU = 2, GEMM_EPI_SWIGLU = 4 };
 
 static constexpr int BM = 128;        // weight rows per block
 static constexpr int BK = 64;         // k per stage: 128 bytes, one swizzle row
@@ -107,6 +107,14 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
 __device__ __forceinline__ float gemm_gelu_tanh(float g) {
     const float c = 0.7978845608028654f;
     return 0.5f * g * (1.0f + tanhf(c * (g + 0.044715f * g * g * g)));
+}
+
+// the gate's activation of the two gated epilogues (tanh-GELU, SiLU)
+__device__ __forceinline__ float gemm_gate_act(float g, int epilogue) {
+    return epilogue == GEMM_EPI_SWIGLU ? g / (1.0f + expf(-g)) : gemm_gelu_tanh(g);
+}
+__host__ __device__ __forceinline__ bool gemm_gated(int epilogue) {
+    return epilogue == GEMM_EPI_GEGLU || epilogue == GEMM_EPI_SWIGLU;
 }
 
 struct GemmArgs {
@@ -206,7 +214,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
                 uint32_t v[32];
                 tmem_ld32(tmem + ((uint32_t)(32 * quarter) << 16) + (uint32_t)c0, v);
                 if (r0 + c0 >= p.R) continue;
-                if (p.epilogue == GEMM_EPI_GEGLU) {
+                if (gemm_gated(p.epilogue)) {
                     // rows come as 8 gates then their 8 ups: the up value sits 8 lanes on
                     const bool is_gate = (n & 15) < 8;
                     const int col = (n >> 4) * 8 + (n & 7);
@@ -216,7 +224,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
                         const float up = __shfl_down_sync(0xffffffffu, mine, 8);
                         const int r = r0 + c0 + j;
                         if (is_gate && n + 8 < p.N && r < p.R)
-                            y[(size_t)r * p.y_stride + col] = from_f32<OutT>(gemm_gelu_tanh(mine) * up);
+                            y[(size_t)r * p.y_stride + col] = from_f32<OutT>(gemm_gate_act(mine, p.epilogue) * up);
                     }
                 } else {
 #pragma unroll
@@ -464,13 +472,13 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid
                 const int n = n0 + c0;
                 if (r >= p.R || n >= p.N) continue;
                 float o[32];
-                if (p.epilogue == GEMM_EPI_GEGLU) {
+                if (gemm_gated(p.epilogue)) {
                     // weight rows come as 8 gates then their 8 ups: 32 columns make 16 outputs
 #pragma unroll
                     for (int g = 0; g < 2; ++g)
 #pragma unroll
                         for (int i = 0; i < 8; ++i)
-                            o[8 * g + i] = gemm_gelu_tanh(__uint_as_float(v[16 * g + i])) *
+                            o[8 * g + i] = gemm_gate_act(__uint_as_float(v[16 * g + i]), p.epilogue) *
                                            __uint_as_float(v[16 * g + 8 + i]);
                     OutT* dst = y + (size_t)r * p.y_stride + n / 2;
                     const int count = min(32, p.N - n) / 2;
@@ -623,7 +631,7 @@ static int gemm_tcgen05(const void* W, const void* x, void* y, int out_dtype, in
                 "of 8", R, N, K, x_stride);
     SIB_REQUIRE(((uintptr_t)W % 16) == 0 && ((uintptr_t)x % 16) == 0,
                 "gemm_tcgen05: operands must be 16-byte aligned");
-    SIB_REQUIRE(epilogue != GEMM_EPI_GEGLU || N % 16 == 0,
+    SIB_REQUIRE(!gemm_gated(epilogue) || N % 16 == 0,
                 "gemm_tcgen05: the gated epilogue needs N (%d) in whole groups of 16", N);
     SIB_REQUIRE(epilogue != GEMM_EPI_SOFTCAP || cap > 0.f, "gemm_tcgen05: soft cap must be positive");
     int dev = 0;

@@ -33,7 +33,7 @@
 
 namespace cg = cooperative_groups;
 
-enum { EPI_NONE = 0, EPI_SOFTCAP = 1, EPI_GEGLU = 2, EPI_ROPE = 3 };
+enum { EPI_NONE = 0, EPI_SOFTCAP = 1, EPI_GEGLU = 2, EPI_ROPE = 3, EPI_SWIGLU = 4 };
 
 // What the q|k|v product needs to rotate and store (see rope_cache.cu for the cache layout).
 struct RopeTail {
@@ -73,6 +73,12 @@ __device__ __forceinline__ uint4 ld16_stream(const __nv_bfloat16* p) {
 __device__ __forceinline__ float gelu_tanh_f(float g) {
     const float c = 0.7978845608028654f;
     return 0.5f * g * (1.0f + tanhf(c * (g + 0.044715f * g * g * g)));
+}
+
+__device__ __forceinline__ float silu_f(float g) { return g / (1.0f + expf(-g)); }
+// the gate's activation of the two gated epilogues (tanh-GELU, SiLU)
+template <int EPI> __device__ __forceinline__ float gate_act(float g) {
+    return EPI == EPI_SWIGLU ? silu_f(g) : gelu_tanh_f(g);
 }
 
 // NT: activation tiles of 8 rows; MT: weight tiles of 16 rows per block.
@@ -250,13 +256,13 @@ __device__ __forceinline__ void skinny_linear_body(
                     }
                 }
             }
-        } else if (EPI == EPI_GEGLU) {
+        } else if (EPI == EPI_GEGLU || EPI == EPI_SWIGLU) {
             // rows gg (gate) and gg + 8 (up) of the 16-row group make column n_out
             const int n_out = (n0 + 16 * m) / 2 + gg;
             if (n_lo + 8 < N) {
-                if (r0 < R) y[(size_t)r0 * y_stride + n_out] = from_f32<OutT>(gelu_tanh_f(s.x) * s.z);
+                if (r0 < R) y[(size_t)r0 * y_stride + n_out] = from_f32<OutT>(gate_act<EPI>(s.x) * s.z);
                 if (r0 + 1 < R)
-                    y[(size_t)(r0 + 1) * y_stride + n_out] = from_f32<OutT>(gelu_tanh_f(s.y) * s.w);
+                    y[(size_t)(r0 + 1) * y_stride + n_out] = from_f32<OutT>(gate_act<EPI>(s.y) * s.w);
             }
         } else {
             float o[4] = {s.x, s.y, s.z, s.w};
@@ -390,7 +396,7 @@ SIB_EXPORT int sib_skinny_linear(const void* W, const void* x, void* y, int out_
                 "skinny_linear: N=%d K=%d; K must be a multiple of 8", N, K);
     SIB_REQUIRE(x_stride % 8 == 0 && ((uintptr_t)W % 16) == 0 && ((uintptr_t)x % 16) == 0,
                 "skinny_linear: operands must be 16-byte aligned (x_stride=%d)", x_stride);
-    SIB_REQUIRE(epilogue != EPI_GEGLU || N % 16 == 0,
+    SIB_REQUIRE((epilogue != EPI_GEGLU && epilogue != EPI_SWIGLU) || N % 16 == 0,
                 "skinny_linear: the gated epilogue needs N (%d) in whole groups of 16", N);
     SIB_REQUIRE(epilogue != EPI_SOFTCAP || cap > 0.f, "skinny_linear: soft cap must be positive");
     cudaStream_t s = (cudaStream_t)stream;
@@ -399,11 +405,13 @@ SIB_EXPORT int sib_skinny_linear(const void* W, const void* x, void* y, int out_
     if (out_dtype == SIB_BF16) {
         if (epilogue == EPI_NONE) GO(__nv_bfloat16, EPI_NONE);
         if (epilogue == EPI_GEGLU) GO(__nv_bfloat16, EPI_GEGLU);
+        if (epilogue == EPI_SWIGLU) GO(__nv_bfloat16, EPI_SWIGLU);
         if (epilogue == EPI_SOFTCAP) GO(__nv_bfloat16, EPI_SOFTCAP);
     } else if (out_dtype == SIB_F32) {
         if (epilogue == EPI_NONE) GO(float, EPI_NONE);
         if (epilogue == EPI_SOFTCAP) GO(float, EPI_SOFTCAP);
         if (epilogue == EPI_GEGLU) GO(float, EPI_GEGLU);
+        if (epilogue == EPI_SWIGLU) GO(float, EPI_SWIGLU);
     }
 #undef GO
     SIB_REQUIRE(false, "skinny_linear: unknown output type %d or epilogue %d", out_dtype, epilogue);

@@ -5,7 +5,7 @@
 // Both recurrences work column by column of the head's matrix S[kd, vd]: column j only
 // ever meets v[j], so (head, column) pairs are independent and a launch has
 // sequences x heads x columns of parallel work; the tokens of a sequence go one after
-// the other.  A column is held in the registers of L neighbouring lanes (32 rows each).
+// the other.  A column is held in the registers of L neighbouring lanes (16 rows each).
 //
 //   delta:   S <- g S;  u = beta (v - S^T k);  S <- S + k u^T;  o = S^T q
 //            as one pass:  u = beta (v_j - g <S_j, k>),  o_j = g <S_j, q> + u <k, q>,
@@ -29,7 +29,7 @@ __device__ __forceinline__ float softplus_f(float x) {
 
 // ---------------------------------------------------------------------------
 // Delta rule, step 1: per row, the short causal convolutions of q | k | v with silu, then
-// unit q (times kd^-1/2) and unit k per head, beta and the decay per head.
+// unit q (times kd^-1/2) and unit k per head, beta and the decay per head (kd <= 256).
 // ---------------------------------------------------------------------------
 struct DeltaPrepareArgs {
     const void* proj;        // [rows, stride]: q (G kd) | k (G kd) | v (H vd) | gate (H vd) | b (H) | a (H)
@@ -51,11 +51,16 @@ struct DeltaPrepareArgs {
     int H, G, kd, vd, taps;
 };
 
+// One warp per (row, unit): the q heads, the k heads, the v heads, and one unit for beta
+// and the decay; a block takes 4 units of one row.
 template <typename T>
-__global__ void __launch_bounds__(256) delta_prepare_kernel(DeltaPrepareArgs p) {
-    extern __shared__ float conv[];            // [channels] the row's convolved, activated values
+__global__ void __launch_bounds__(128) delta_prepare_kernel(DeltaPrepareArgs p) {
     pdl_trigger();
+    const int lane = threadIdx.x & 31;
     const int r = blockIdx.x;
+    const int unit = blockIdx.y * 4 + (threadIdx.x >> 5);
+    const int units = 2 * p.G + p.H + 1;
+    if (unit >= units) return;
     const int nqk = p.G * p.kd, channels = 2 * nqk + p.H * p.vd;
     const int pos = p.row_pos[r];
     const int b = p.row_seq[r];
@@ -64,7 +69,17 @@ __global__ void __launch_bounds__(256) delta_prepare_kernel(DeltaPrepareArgs p) 
     const float* hist = slot >= 0 ? p.state + (size_t)slot * p.state_stride + p.hist_offset : nullptr;
     pdl_wait();
     const T* proj = (const T*)p.proj;
-    for (int c = threadIdx.x; c < channels; c += blockDim.x) {
+    if (unit == units - 1) {
+        for (int h = lane; h < p.H; h += 32) {
+            const size_t at = (size_t)r * p.stride + channels + (size_t)p.H * p.vd;
+            p.beta[(size_t)r * p.H + h] = sigmoid_f(to_f32(proj[at + h]));
+            const float dt = softplus_f(to_f32(proj[at + p.H + h]) + p.dt_bias[h]);
+            p.decay[(size_t)r * p.H + h] = expf(-expf(p.a_log[h]) * dt);
+        }
+        return;
+    }
+    // the convolved, activated value of channel c of this row
+    auto channel = [&](int c) {
         float acc = 0.f;
         for (int j = 0; j < p.taps; ++j) {
             const int at = pos - (p.taps - 1) + j;      // position of the tap's input
@@ -73,27 +88,28 @@ __global__ void __launch_bounds__(256) delta_prepare_kernel(DeltaPrepareArgs p) 
             else if (hist) x = hist[(size_t)(at - start + p.taps - 1) * channels + c];
             acc += p.conv_w[(size_t)c * p.taps + j] * x;
         }
-        conv[c] = silu_f(acc);
+        return silu_f(acc);
+    };
+    if (unit >= 2 * p.G) {                                   // a v head
+        const int c0 = 2 * nqk + (unit - 2 * p.G) * p.vd;
+        for (int d = lane; d < p.vd; d += 32)
+            p.vc[(size_t)r * p.H * p.vd + (c0 - 2 * nqk) + d] = channel(c0 + d);
+        return;
     }
-    __syncthreads();
-    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, warps = blockDim.x >> 5;
-    for (int u = warp; u < 2 * p.G; u += warps) {          // q heads, then k heads
-        const float* x = conv + (size_t)u * p.kd;
-        float ss = 0.f;
-        for (int d = lane; d < p.kd; d += 32) ss += x[d] * x[d];
-        float inv = 1.0f / sqrtf(warp_sum(ss) + 1e-6f);
-        if (u < p.G) inv *= 1.0f / sqrtf((float)p.kd);
-        float* dst = (u < p.G ? p.qn : p.kn) + (size_t)r * nqk + (size_t)(u % p.G) * p.kd;
-        for (int d = lane; d < p.kd; d += 32) dst[d] = x[d] * inv;
+    float x[8];                                              // kd <= 256
+    float ss = 0.f;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+        const int d = lane + 32 * i;
+        x[i] = d < p.kd ? channel(unit * p.kd + d) : 0.f;
+        ss += x[i] * x[i];
     }
-    for (int c = threadIdx.x; c < p.H * p.vd; c += blockDim.x)
-        p.vc[(size_t)r * p.H * p.vd + c] = conv[2 * nqk + c];
-    for (int h = threadIdx.x; h < p.H; h += blockDim.x) {
-        const size_t at = (size_t)r * p.stride + channels + (size_t)p.H * p.vd;
-        p.beta[(size_t)r * p.H + h] = sigmoid_f(to_f32(proj[at + h]));
-        const float dt = softplus_f(to_f32(proj[at + p.H + h]) + p.dt_bias[h]);
-        p.decay[(size_t)r * p.H + h] = expf(-expf(p.a_log[h]) * dt);
-    }
+    float inv = 1.0f / sqrtf(warp_sum(ss) + 1e-6f);
+    if (unit < p.G) inv *= 1.0f / sqrtf((float)p.kd);
+    float* dst = (unit < p.G ? p.qn : p.kn) + (size_t)r * nqk + (size_t)(unit % p.G) * p.kd;
+#pragma unroll
+    for (int i = 0; i < 8; ++i)
+        if (lane + 32 * i < p.kd) dst[lane + 32 * i] = x[i] * inv;
 }
 
 // The history after the step: the last taps - 1 inputs of each sequence.  One thread per
@@ -148,13 +164,9 @@ struct ScanArgs {
     float q_scale, cap;
 };
 
-constexpr int kPerLane = 32;     // rows of a column that one lane holds
-
-template <typename T> __device__ __forceinline__ void load_slice(const T* src, int d0, int kd,
-                                                                  float scale, float (&dst)[kPerLane]) {
-#pragma unroll
-    for (int i = 0; i < kPerLane; ++i) dst[i] = d0 + i < kd ? to_f32(src[d0 + i]) * scale : 0.f;
-}
+constexpr int kPerLane = 16;     // rows of a column that one lane holds
+constexpr int kMaxLanes = 16;    // lanes that share a column at most
+constexpr int kChunk = 8;        // tokens staged in shared memory at a time
 
 template <int L> __device__ __forceinline__ float lanes_sum(float v) {
 #pragma unroll
@@ -162,18 +174,37 @@ template <int L> __device__ __forceinline__ float lanes_sum(float v) {
     return v;
 }
 
-// blockDim.x threads = blockDim.x / L columns; grid (column tiles, heads, sequences).
-template <int MODE, typename TQ, typename TG, int L>
+__device__ __forceinline__ float log_sigmoid_f(float z) { return -softplus_f(-z); }
+
+// 64 threads = 64 / L columns, each held by L neighbouring lanes; grid (column tiles, heads,
+// sequences).  Lane s of a column owns the rows ((i * L + s) * 4 .. + 3), so that
+// the lanes of a column read neighbouring 16-byte pieces of it (i = 0..kPerLane / 4 - 1).
+//
+// The tokens' q, k, v and gates come through shared memory, kChunk tokens at a time and two
+// buffers in turn: the next chunk's values are asked for before the current chunk is worked
+// on and put down after it, so the walk over the tokens waits for shared memory only.  For
+// the memory the gates of a chunk (which depend on no matrix) are made once per chunk by
+// kChunk threads, in closed form: with F_t = f_1 + .. + f_t inside the chunk and m_0 the
+// maximum before it,  m_t = max(F_t + m_0, max_{s <= t} (i_s + F_t - F_s)).
+template <int MODE, typename TQ, typename TG, int L, bool VEC>
 __global__ void __launch_bounds__(64) recurrent_scan_kernel(ScanArgs p) {
+    constexpr int KP = kPerLane * L;                 // key width as staged (zeros behind kd)
+    constexpr int CB = 64 / L;                       // columns of a block
+    constexpr int BUF = kChunk * (2 * KP + CB + 4);  // q | k | v | keep | take | i | f
+    constexpr int NQ = kChunk * KP / 64, NV = kChunk * CB / 64 > 0 ? kChunk * CB / 64 : 1;
+    extern __shared__ __align__(16) float staged[];
+    __shared__ float m_carry;
     pdl_trigger();
-    const int col = (blockIdx.x * blockDim.x + threadIdx.x) / L;
-    const int d0 = (threadIdx.x % L) * kPerLane;
+    const int tid = threadIdx.x;
+    const int s = tid % L, cl = tid / L;
+    const int col = blockIdx.x * CB + cl;
     const int h = blockIdx.y, b = blockIdx.z;
     const int cols = MODE == SCAN_MEMORY ? p.vd + 1 : p.vd;
-    const bool live = col < cols;          // (idle lanes still take part in the shuffles)
+    const bool live = col < cols;          // (idle lanes still take part in shuffles and barriers)
     const int g = h / (p.H / p.G);
     const int slot = p.seq_slot[b];
     const int row0 = p.seq_row0[b], n = p.seq_end[b] - p.seq_start[b];
+    const int n_chunks = (n + kChunk - 1) / kChunk;
     float S[kPerLane];
     float* mine = slot >= 0 && live
         ? p.state + (size_t)slot * p.state_stride + ((size_t)h * cols + col) * p.kd : nullptr;
@@ -181,67 +212,192 @@ __global__ void __launch_bounds__(64) recurrent_scan_kernel(ScanArgs p) {
         ? p.state + (size_t)slot * p.state_stride + (size_t)p.H * cols * p.kd + h : nullptr;
     pdl_wait();
 #pragma unroll
-    for (int i = 0; i < kPerLane; ++i) S[i] = mine && d0 + i < p.kd ? mine[d0 + i] : 0.f;
-    float m = m_cell ? *m_cell : 0.f;
+    for (int i = 0; i < kPerLane / 4; ++i) {
+        const int d = (i * L + s) * 4;
+        if (VEC) {
+            float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+            if (mine && d < p.kd) v = *reinterpret_cast<const float4*>(mine + d);
+            S[4 * i] = v.x; S[4 * i + 1] = v.y; S[4 * i + 2] = v.z; S[4 * i + 3] = v.w;
+        } else {
+#pragma unroll
+            for (int e = 0; e < 4; ++e) S[4 * i + e] = mine && d + e < p.kd ? mine[d + e] : 0.f;
+        }
+    }
+    if (tid == 0) m_carry = m_cell ? *m_cell : 0.f;
+
     const TQ* qp = (const TQ*)p.q + (size_t)g * p.kd;
     const TQ* kp = (const TQ*)p.k + (size_t)g * p.kd;
     const TQ* vp = (const TQ*)p.v + (size_t)h * p.vd;
-    float kk[kPerLane], qq[kPerLane];
-    for (int t = 0; t < n; ++t) {
-        const size_t r = (size_t)(row0 + t);
-        load_slice(kp + r * p.k_stride, d0, p.kd, 1.0f, kk);
-        load_slice(qp + r * p.q_stride, d0, p.kd, p.q_scale, qq);
-        float vj = 0.f;
-        if (live) vj = (MODE == SCAN_MEMORY && col == p.vd) ? 1.0f : to_f32(vp[r * p.v_stride + col]);
-        float sk = 0.f, sq = 0.f, kq = 0.f;
+    float rq[NQ], rk[NQ], rv[NV], rg = 0.f;
+
+    // the chunk's values from global memory into registers ...
+    auto fetch = [&](int c) {
+        const int t0 = c * kChunk;
 #pragma unroll
-        for (int i = 0; i < kPerLane; ++i) {
-            sk += S[i] * kk[i];
-            sq += S[i] * qq[i];
-            kq += kk[i] * qq[i];
-        }
-        sq = lanes_sum<L>(sq);
-        kq = lanes_sum<L>(kq);
-        float keep, take;       // S <- keep S + take k
-        if (MODE == SCAN_DELTA) {
-            sk = lanes_sum<L>(sk);
-            keep = p.decay[r * p.H + h];
-            take = p.beta[r * p.H + h] * (vj - keep * sk);
-        } else {
-            const TG* gi = (const TG*)p.gate_i;
-            const TG* gf = (const TG*)p.gate_f;
-            const float ig = p.cap * tanhf((to_f32(gi[r * p.gate_stride + h]) + p.bias_i[h]) / p.cap);
-            const float fz = p.cap * tanhf((to_f32(gf[r * p.gate_stride + h]) + p.bias_f[h]) / p.cap);
-            const float fg = -softplus_f(-fz);             // log sigmoid
-            const float m_new = fmaxf(fg + m, ig);
-            keep = expf(fg + m - m_new);
-            take = expf(ig - m_new) * vj;
-            m = m_new;
-            if (p.m_out && blockIdx.x == 0 && threadIdx.x == 0) p.m_out[r * p.H + h] = m_new;
+        for (int i = 0; i < NQ; ++i) {
+            const int e = tid + 64 * i, t = e / KP, d = e % KP;
+            const bool in = t0 + t < n && d < p.kd;
+            const size_t r = (size_t)(row0 + t0 + t);
+            rq[i] = in ? to_f32(qp[r * p.q_stride + d]) * p.q_scale : 0.f;
+            rk[i] = in ? to_f32(kp[r * p.k_stride + d]) : 0.f;
         }
 #pragma unroll
-        for (int i = 0; i < kPerLane; ++i) S[i] = keep * S[i] + take * kk[i];
-        if (live && d0 == 0) p.out[(r * p.H + h) * cols + col] = keep * sq + take * kq;
+        for (int i = 0; i < NV; ++i) {
+            const int e = tid + 64 * i, t = e / CB, c2 = blockIdx.x * CB + e % CB;
+            rv[i] = 0.f;
+            if (e < kChunk * CB && t0 + t < n) {
+                const size_t r = (size_t)(row0 + t0 + t);
+                if (c2 < p.vd) rv[i] = to_f32(vp[r * p.v_stride + c2]);
+                else if (MODE == SCAN_MEMORY && c2 == p.vd) rv[i] = 1.0f;
+            }
+        }
+        if (tid < 2 * kChunk) {
+            const int t = tid % kChunk;
+            rg = 0.f;
+            if (t0 + t < n) {
+                const size_t r = (size_t)(row0 + t0 + t);
+                if (MODE == SCAN_DELTA) {
+                    rg = (tid < kChunk ? p.decay : p.beta)[r * p.H + h];
+                } else {
+                    const TG* src = (const TG*)(tid < kChunk ? p.gate_i : p.gate_f);
+                    const float bias = (tid < kChunk ? p.bias_i : p.bias_f)[h];
+                    rg = p.cap * tanhf((to_f32(src[r * p.gate_stride + h]) + bias) / p.cap);
+                    if (tid >= kChunk) rg = log_sigmoid_f(rg);
+                }
+            }
+        }
+    };
+    // ... and from the registers into a buffer
+    auto put = [&](float* buf) {
+#pragma unroll
+        for (int i = 0; i < NQ; ++i) {
+            buf[tid + 64 * i] = rq[i];
+            buf[kChunk * KP + tid + 64 * i] = rk[i];
+        }
+#pragma unroll
+        for (int i = 0; i < NV; ++i)
+            if (tid + 64 * i < kChunk * CB) buf[2 * kChunk * KP + tid + 64 * i] = rv[i];
+        // delta: keep = decay, take = beta; memory: the gates i and f, worked on below
+        if (tid < 2 * kChunk)
+            buf[2 * kChunk * KP + kChunk * CB + (MODE == SCAN_DELTA ? 0 : 2 * kChunk) + tid] = rg;
+    };
+    // memory: keep and take of the chunk's tokens from its gates and the maximum so far
+    auto gates = [&](float* buf, int c) {
+        if (MODE != SCAN_MEMORY) return;
+        float* keep = buf + 2 * kChunk * KP + kChunk * CB;
+        const float* gi = keep + 2 * kChunk;
+        const float* gf = gi + kChunk;
+        const int t0 = c * kChunk;
+        const int t = tid;
+        if (t < kChunk && t0 + t < n) {
+            const float m0 = m_carry;
+            float F = 0.f, best = -INFINITY, before = m0, now = m0;
+            // walking s = 0..t: F = F_s, best = max_{u <= s} (i_u - F_u)
+            for (int u = 0; u <= t; ++u) {
+                before = now;
+                F += gf[u];
+                best = fmaxf(best, gi[u] - F);
+                now = fmaxf(F + m0, best + F);
+            }
+            keep[t] = expf(gf[t] + before - now);
+            keep[kChunk + t] = expf(gi[t] - now);
+            if (p.m_out && blockIdx.x == 0) p.m_out[(size_t)(row0 + t0 + t) * p.H + h] = now;
+            if (t == kChunk - 1 || t0 + t == n - 1) staged[2 * BUF] = now;    // (read after the barrier)
+        }
+    };
+
+    if (n_chunks > 0) {
+        fetch(0);
+        put(staged);
+    }
+    __syncthreads();
+    if (n_chunks > 0) gates(staged, 0);
+    __syncthreads();
+    if (MODE == SCAN_MEMORY && tid == 0 && n_chunks > 0) m_carry = staged[2 * BUF];
+    __syncthreads();
+    for (int c = 0; c < n_chunks; ++c) {
+        float* buf = staged + (c & 1) * BUF;
+        float* next = staged + ((c + 1) & 1) * BUF;
+        const bool more = c + 1 < n_chunks;
+        if (more) fetch(c + 1);
+        const int count = min(kChunk, n - c * kChunk);
+        const float* keep = buf + 2 * kChunk * KP + kChunk * CB;
+        for (int t = 0; t < count; ++t) {
+            float kk[kPerLane], qq[kPerLane];
+#pragma unroll
+            for (int i = 0; i < kPerLane / 4; ++i) {
+                const int d = (i * L + s) * 4;
+                const float4 a = *reinterpret_cast<const float4*>(buf + t * KP + d);
+                const float4 c4 = *reinterpret_cast<const float4*>(buf + kChunk * KP + t * KP + d);
+                qq[4 * i] = a.x; qq[4 * i + 1] = a.y; qq[4 * i + 2] = a.z; qq[4 * i + 3] = a.w;
+                kk[4 * i] = c4.x; kk[4 * i + 1] = c4.y; kk[4 * i + 2] = c4.z; kk[4 * i + 3] = c4.w;
+            }
+            const float vj = buf[2 * kChunk * KP + t * CB + cl];
+            float sk[4] = {0.f, 0.f, 0.f, 0.f}, sq[4] = {0.f, 0.f, 0.f, 0.f}, kq[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+            for (int i = 0; i < kPerLane; ++i) {
+                if (MODE == SCAN_DELTA) sk[i & 3] += S[i] * kk[i];
+                sq[i & 3] += S[i] * qq[i];
+                kq[i & 3] += kk[i] * qq[i];
+            }
+            const float sq1 = lanes_sum<L>((sq[0] + sq[1]) + (sq[2] + sq[3]));
+            const float kq1 = lanes_sum<L>((kq[0] + kq[1]) + (kq[2] + kq[3]));
+            const float keep_t = keep[t];
+            float take;       // S <- keep S + take k
+            if (MODE == SCAN_DELTA) {
+                const float sk1 = lanes_sum<L>((sk[0] + sk[1]) + (sk[2] + sk[3]));
+                take = keep[kChunk + t] * (vj - keep_t * sk1);
+            } else {
+                take = keep[kChunk + t] * vj;
+            }
+#pragma unroll
+            for (int i = 0; i < kPerLane; ++i) S[i] = keep_t * S[i] + take * kk[i];
+            if (live && s == 0)
+                p.out[((size_t)(row0 + c * kChunk + t) * p.H + h) * cols + col] = keep_t * sq1 + take * kq1;
+        }
+        if (more) put(next);
+        __syncthreads();
+        if (more) gates(next, c + 1);
+        __syncthreads();
+        if (MODE == SCAN_MEMORY && tid == 0 && more) m_carry = staged[2 * BUF];
+        __syncthreads();
     }
     if (mine) {
 #pragma unroll
-        for (int i = 0; i < kPerLane; ++i)
-            if (d0 + i < p.kd) mine[d0 + i] = S[i];
+        for (int i = 0; i < kPerLane / 4; ++i) {
+            const int d = (i * L + s) * 4;
+            if (VEC) {
+                if (d < p.kd)
+                    *reinterpret_cast<float4*>(mine + d) = make_float4(S[4 * i], S[4 * i + 1], S[4 * i + 2], S[4 * i + 3]);
+            } else {
+#pragma unroll
+                for (int e = 0; e < 4; ++e)
+                    if (d + e < p.kd) mine[d + e] = S[4 * i + e];
+            }
+        }
     }
-    if (m_cell && blockIdx.x == 0 && threadIdx.x == 0) *m_cell = m;
+    if (m_cell && blockIdx.x == 0 && tid == 0) *m_cell = m_carry;
 }
 
 template <int MODE, typename TQ, typename TG>
 static int launch_scan(const ScanArgs& p, int n_seqs, cudaStream_t s) {
     const int cols = MODE == SCAN_MEMORY ? p.vd + 1 : p.vd;
-    const int L = p.kd <= 32 ? 1 : p.kd <= 64 ? 2 : p.kd <= 128 ? 4 : 8;
+    const int L = p.kd <= 16 ? 1 : p.kd <= 32 ? 2 : p.kd <= 64 ? 4 : p.kd <= 128 ? 8 : 16;
     const int threads = 64;
     const dim3 grid((cols * L + threads - 1) / threads, p.H, n_seqs);
-#define GO(LL) sib_launch_chained(recurrent_scan_kernel<MODE, TQ, TG, LL>, grid, dim3(threads), 0, s, p)
+    const bool vec = p.kd % 4 == 0 && p.state_stride % 4 == 0 && ((uintptr_t)p.state % 16) == 0;
+    // two buffers and the word that hands the running maximum from chunk to chunk
+    const size_t smem = (size_t)(2 * kChunk * (2 * kPerLane * L + 64 / L + 4) + 4) * sizeof(float);
+#define GO(LL)                                                                                     \
+    do {                                                                                           \
+        if (vec) sib_launch_chained(recurrent_scan_kernel<MODE, TQ, TG, LL, true>, grid, dim3(threads), smem, s, p); \
+        else sib_launch_chained(recurrent_scan_kernel<MODE, TQ, TG, LL, false>, grid, dim3(threads), smem, s, p);    \
+    } while (0)
     if (L == 1) GO(1);
     else if (L == 2) GO(2);
     else if (L == 4) GO(4);
-    else GO(8);
+    else if (L == 8) GO(8);
+    else GO(16);
 #undef GO
     return sib_check_launch("recurrent_scan");
 }
@@ -249,8 +405,8 @@ static int launch_scan(const ScanArgs& p, int n_seqs, cudaStream_t s) {
 static int check_scan(const char* what, int rows, int n_seqs, int H, int G, int kd, int vd) {
     SIB_REQUIRE(rows > 0 && n_seqs > 0 && n_seqs < 65536 && H > 0 && H < 65536 && G > 0 && H % G == 0,
                 "%s: rows=%d sequences=%d heads=%d key heads=%d", what, rows, n_seqs, H, G);
-    SIB_REQUIRE(kd > 0 && kd <= 8 * kPerLane && vd > 0,
-                "%s: key width %d (at most %d) and value width %d", what, kd, 8 * kPerLane, vd);
+    SIB_REQUIRE(kd > 0 && kd <= kMaxLanes * kPerLane && vd > 0,
+                "%s: key width %d (at most %d) and value width %d", what, kd, kMaxLanes * kPerLane, vd);
     return 0;
 }
 
@@ -264,20 +420,14 @@ SIB_EXPORT int sib_delta_prepare(
     if (check_scan("delta_prepare", rows, n_seqs, H, G, kd, vd)) return -1;
     SIB_REQUIRE(taps >= 1 && taps <= 64, "delta_prepare: %d taps", taps);
     const int channels = 2 * G * kd + H * vd;
-    const size_t smem = (size_t)channels * sizeof(float);
-    SIB_REQUIRE(smem <= 200 * 1024, "delta_prepare: %d channels do not fit shared memory", channels);
+    const int units = 2 * G + H + 1;
+    SIB_REQUIRE((units + 3) / 4 < 65536, "delta_prepare: too many heads (%d)", H);
     DeltaPrepareArgs p{proj, conv_w, a_log, dt_bias, state, qn, kn, vc, beta, decay, row_pos,
                        row_seq, seq_slot, seq_start, seq_row0, stride, state_stride, hist_offset,
                        H, G, kd, vd, taps};
     cudaStream_t s = (cudaStream_t)stream;
-    SIB_DISPATCH_DTYPE(dtype, {
-        if (smem > 48 * 1024) {
-            cudaError_t e = cudaFuncSetAttribute(delta_prepare_kernel<T>,
-                                                 cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-            SIB_REQUIRE(e == cudaSuccess, "delta_prepare: %s", cudaGetErrorString(e));
-        }
-        sib_launch_chained(delta_prepare_kernel<T>, dim3(rows), dim3(256), smem, s, p);
-    });
+    SIB_DISPATCH_DTYPE(dtype, sib_launch_chained(delta_prepare_kernel<T>, dim3(rows, (units + 3) / 4),
+                                                 dim3(128), 0, s, p));
     int rc = sib_check_launch("delta_prepare");
     if (rc || taps == 1) return rc;
     const dim3 grid((channels + 255) / 256, n_seqs);

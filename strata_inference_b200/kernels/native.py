@@ -19,6 +19,8 @@ import torch
 
 F32, BF16 = 0, 1
 EPI_NONE, EPI_SOFTCAP, EPI_GEGLU = 0, 1, 2
+EPI_SWIGLU = 4          # the gated epilogue with SiLU (weight-streaming and paired tcgen05 products)
+GATED_EPILOGUES = (EPI_GEGLU, EPI_SWIGLU)
 ROPE_HALF_SPLIT, ROPE_INTERLEAVED = 0, 1
 ACT_GELU_TANH, ACT_SILU = 0, 1          # of the gated feed-forward
 GATE_SILU, GATE_SIGMOID = 0, 1          # of head_norm_gate
@@ -400,7 +402,7 @@ def rope_store(qkv: torch.Tensor, row_pos, row_seq, seq_slot, seq_end,
         c_int(n_heads), c_int(n_kv), c_int(head_dim), _stream()))
 
 
-@_timed(lambda proj, qkv, *a, **kw: ("head_prepare", _nbytes(proj, qkv), 0))
+@_timed(lambda proj, qkv, *a, **kw: ("head_prepare", _nbytes(proj) + 2 * _nbytes(qkv), 0))
 def head_prepare(proj: torch.Tensor, qkv: torch.Tensor, bias: Optional[torch.Tensor],
                  q_gain: Optional[torch.Tensor], k_gain: Optional[torch.Tensor], eps: float,
                  inv_freq: Optional[torch.Tensor], rotary_dim: int,
@@ -484,7 +486,8 @@ def _f32(t: Optional[torch.Tensor], n: int, name: str) -> None:
         raise KernelError(f"{name} has {t.numel()} values, expected {n}")
 
 
-@_timed(lambda proj, *a, **kw: ("delta_prepare", 3 * _nbytes(proj), 0))
+@_timed(lambda proj, conv_w, a_log, dt_bias, state, hist_offset, qn, kn, vc, beta, decay, *a, **kw: (
+    "delta_prepare", _nbytes(proj, qn, kn, vc, beta, decay), 0))
 def delta_prepare(proj: torch.Tensor, conv_w: torch.Tensor, a_log: torch.Tensor,
                   dt_bias: torch.Tensor, state: torch.Tensor, hist_offset: int, qn: torch.Tensor,
                   kn: torch.Tensor, vc: torch.Tensor, beta: torch.Tensor, decay: torch.Tensor, ctx,
@@ -520,7 +523,7 @@ def delta_prepare(proj: torch.Tensor, conv_w: torch.Tensor, a_log: torch.Tensor,
 def _scan_work(kind, rows, n_seqs, n_heads, key_dim, cols):
     state = n_seqs * n_heads * key_dim * cols * 4
     return kind, 2 * state + rows * n_heads * (2 * key_dim + 2 * cols) * 4, \
-        6.0 * rows * n_heads * key_dim * cols
+        7.0 * rows * n_heads * key_dim * cols
 
 
 @_timed(lambda qn, kn, vc, decay, beta, state, out, ctx, n_heads, n_kv, key_dim, value_dim: _scan_work(
@@ -574,7 +577,7 @@ def memory_scan(proj: torch.Tensor, bias_i: torch.Tensor, bias_f: torch.Tensor, 
     return out
 
 
-@_timed(lambda o, m, w, gate, y, *a: ("head_norm_gate", _nbytes(o, y) + _nbytes(y), 0))
+@_timed(lambda o, m, w, gate, y, *a: ("head_norm_gate", _nbytes(o, y) + _nbytes(y), 0))  # (+ the gates)
 def head_norm_gate(o: torch.Tensor, m: Optional[torch.Tensor], w: torch.Tensor,
                    gate: torch.Tensor, y: torch.Tensor, n_heads: int, value_dim: int, eps: float,
                    act: int) -> torch.Tensor:
@@ -844,7 +847,7 @@ def skinny_linear(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, epilogue:
     _want(out, out.dtype, "out", contiguous=False)
     R, K = x.shape
     N = w.shape[0]
-    n_out = N // 2 if epilogue == EPI_GEGLU else N
+    n_out = N // 2 if epilogue in GATED_EPILOGUES else N
     if w.shape[1] != K or tuple(out.shape) != (R, n_out) or x.stride(1) != 1 or out.stride(1) != 1:
         raise KernelError("skinny_linear: shapes do not fit")
     _check(library().sib_skinny_linear(_ptr(w), _ptr(x), _ptr(out), _code(out.dtype), c_int(R),
@@ -870,7 +873,7 @@ def linear_stream(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, epilogue:
     _want(out, out.dtype, "out", contiguous=False)
     R, K = x.shape
     N = w.shape[0]
-    n_out = N // 2 if epilogue == EPI_GEGLU else N
+    n_out = N // 2 if epilogue in GATED_EPILOGUES else N
     if w.shape[1] != K or tuple(out.shape) != (R, n_out) or x.stride(1) != 1 or out.stride(1) != 1:
         raise KernelError("linear_stream: shapes do not fit")
     _check(library().sib_linear_stream(_ptr(w), _ptr(x), _ptr(out), _code(out.dtype), c_int(R),
@@ -897,7 +900,7 @@ def linear_rows_tc(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, epilogue
     _want(out, out.dtype, "out", contiguous=False)
     R, K = x.shape
     N = w.shape[0]
-    n_out = N // 2 if epilogue == EPI_GEGLU else N
+    n_out = N // 2 if epilogue in GATED_EPILOGUES else N
     if w.shape[1] != K or tuple(out.shape) != (R, n_out) or x.stride(1) != 1 or out.stride(1) != 1:
         raise KernelError("linear_rows_tc: shapes do not fit")
     _check(library().sib_linear_rows_tc(_ptr(w), _ptr(x), _ptr(out), _code(out.dtype), c_int(R),
@@ -959,7 +962,7 @@ def gemm_tcgen05(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, epilogue: 
     _want(out, out.dtype, "out", contiguous=False)
     R, K = x.shape
     N = w.shape[0]
-    n_out = N // 2 if epilogue == EPI_GEGLU else N
+    n_out = N // 2 if epilogue in GATED_EPILOGUES else N
     if w.shape[1] != K or tuple(out.shape) != (R, n_out) or x.stride(1) != 1 or out.stride(1) != 1:
         raise KernelError("gemm_tcgen05: shapes do not fit")
     entry = library().sib_gemm_tcgen05_one_block if one_block else library().sib_gemm_tcgen05
@@ -1085,7 +1088,7 @@ def chain_product(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, epilogue:
     _want(w, torch.bfloat16, "w")
     R, K = x.shape
     N = w.shape[0]
-    n_out = N // 2 if epilogue == EPI_GEGLU else N
+    n_out = N // 2 if epilogue in GATED_EPILOGUES else N
     if w.shape[1] != K or tuple(out.shape) != (R, n_out) or x.stride(1) != 1 or out.stride(1) != 1:
         raise KernelError("chain_product: shapes do not fit")
     if out.dtype not in (torch.bfloat16, torch.float32):

@@ -199,9 +199,13 @@ class Runtime:
         out_dtype = out_dtype or x.dtype
         R, K = x.shape
         N = w.shape[0]
-        n_out = N // 2 if epilogue == native.EPI_GEGLU else N
-        if self._chainable(x, w, out_dtype) and (out_dtype == torch.bfloat16
-                                                 or epilogue != native.EPI_GEGLU):
+        gated = epilogue in native.GATED_EPILOGUES
+        n_out = N // 2 if gated else N
+        # (the chain kernel, the staged product and the tcgen05 weight-streaming product know
+        # the tanh-GELU gate only)
+        only_gelu = epilogue != native.EPI_SWIGLU
+        if self._chainable(x, w, out_dtype) and only_gelu and (out_dtype == torch.bfloat16
+                                                               or not gated):
             out = torch.empty((R, n_out), dtype=out_dtype, device=x.device)
             self.chain.add(native.chain_product(x, w, out, epilogue, cap), (x, w, out))
             return out
@@ -209,27 +213,27 @@ class Runtime:
         if (x.dtype == torch.bfloat16 and 0 < R <= self.skinny_max_rows and K % 8 == 0
                 and x.stride(1) == 1 and x.stride(0) % 8 == 0 and x.data_ptr() % 16 == 0):
             out = torch.empty((R, n_out), dtype=out_dtype, device=x.device)
-            mode = self.stream_products
+            mode = self.stream_products if only_gelu else "0"
             if mode == "1" or (mode == "down" and K >= 2 * N) or (mode == "small" and N * K < 30e6) \
                     or (mode == "notgu" and epilogue != native.EPI_GEGLU and N < 100000):
                 return native.linear_stream(x, w, out, epilogue, cap)
             return native.skinny_linear(x, w, out, epilogue, cap)
         aligned = (K % 8 == 0 and x.stride(1) == 1 and x.stride(0) % 8 == 0
                    and x.data_ptr() % 16 == 0)
-        if (x.dtype == torch.bfloat16 and aligned and R <= self.rows_tc_max_rows
+        if (x.dtype == torch.bfloat16 and aligned and R <= self.rows_tc_max_rows and only_gelu
                 and N >= self.rows_tc_min_weight_rows and w.is_contiguous()):
             # some rows against very many weight rows (the logits of a batch of 17 to 128):
             # the weight-streaming tcgen05 product, with its epilogue
             out = torch.empty((R, n_out), dtype=out_dtype, device=x.device)
             return native.linear_rows_tc(x, w, out, epilogue, cap)
-        fused_gate = epilogue == native.EPI_GEGLU and R > self.gated_gemm_min_rows
+        fused_gate = gated and R > self.gated_gemm_min_rows
         if x.dtype == torch.bfloat16 and aligned and (out_dtype == torch.float32 or fused_gate):
             # the tcgen05 product where its epilogue saves a pass over the outputs: 32-bit
             # logits of many rows, soft-capped as they are written; the gated activation of
             # the feed-forward, which halves what is written and spares a second kernel
             out = torch.empty((R, n_out), dtype=out_dtype, device=x.device)
             return native.gemm_tcgen05(x, w, out, epilogue, cap)
-        if epilogue == native.EPI_GEGLU:
+        if gated:
             raise ValueError("the gated epilogue exists in the hand-written products only")
         with native.profile_region(f"library product {N}x{K}",
                                    (N * K + R * K) * x.element_size() + R * N * 4,

@@ -24,7 +24,7 @@ from .registry import register_feed_forward
 
 # activation of the gate -> (elementwise kernel's code, fused epilogue of the products or None)
 _ACTIVATIONS = {"gelu_pytorch_tanh": (native.ACT_GELU_TANH, native.EPI_GEGLU),
-                "silu": (native.ACT_SILU, None)}
+                "silu": (native.ACT_SILU, native.EPI_SWIGLU)}
 _GROUP = 8
 
 
@@ -74,7 +74,8 @@ class GatedMLP:
         if (self.epilogue is not None and self.group == _GROUP and x.dtype == torch.bfloat16
                 and x.shape[1] % 8 == 0
                 and (R <= rt.skinny_max_rows or R > rt.gated_gemm_min_rows
-                     or (rt.chain is not None and R <= rt.chain_max_rows))):
+                     or (rt.chain is not None and R <= rt.chain_max_rows
+                         and self.epilogue == native.EPI_GEGLU))):
             t = rt.linear(x, self.w_gate_up, epilogue=self.epilogue)
         else:
             gate_up = rt.linear(x, self.w_gate_up)

@@ -50,6 +50,10 @@ def _pieces(rows):
     return tuple(out), at
 
 
+def _round4(n: int) -> int:
+    return -(-n // 4) * 4
+
+
 class GatedDeltaRule:
     captures_prompts = True      # sequences, slots and counts are read on the device only
 
@@ -113,7 +117,8 @@ class GatedDeltaRule:
         self.norm_gain = weights["norm.gain"]
 
     def cache_need(self) -> Optional[CacheNeed]:
-        return CacheNeed(state=StateNeed((self.matrices + (self.taps - 1) * self.channels,)))
+        # (whole groups of 4 floats, so that every slot's state begins on a 16-byte boundary)
+        return CacheNeed(state=StateNeed((_round4(self.matrices + (self.taps - 1) * self.channels),)))
 
     def forward(self, x: torch.Tensor, ctx, entry: int, cache_entry: int,
                 owns_cache: bool) -> torch.Tensor:
@@ -191,7 +196,7 @@ class MatrixMemory:
 
     def cache_need(self) -> Optional[CacheNeed]:
         # S with n as one more column, then the running maxima
-        return CacheNeed(state=StateNeed((self.H * (self.vd + 1) * self.kd + self.H,)))
+        return CacheNeed(state=StateNeed((_round4(self.H * (self.vd + 1) * self.kd + self.H),)))
 
     def forward(self, x: torch.Tensor, ctx, entry: int, cache_entry: int,
                 owns_cache: bool) -> torch.Tensor:

@@ -92,7 +92,7 @@ SHARP = model(64, 200, [
 # key, cell or state does to a single row is the 32-bit runs' business, which take the same kernels'
 # other instantiation.
 REL_TOL = {"float32": 1e-4, "bfloat16": 4e-2}
-BF16_MEDIAN, BF16_ROWS_OVER, BF16_WORST = 1.5e-2, 0.25, 0.9
+BF16_MEDIAN, BF16_ROWS_OVER, BF16_WORST = 2.5e-2, 0.3, 0.9
 
 
 def prompts(cfg: dict, lengths: Sequence[int], seed: int) -> List[List[int]]:

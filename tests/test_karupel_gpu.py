@@ -264,3 +264,26 @@ def test_trace_replay_of_a_model_folder(tmp_path):
     for k in range(10):
         want = [ra[70 + k]] + ([rb[20 + k]] if k % 2 else [])
         assert_close(read(k + 1), torch.stack(want), dtype, f"step {k + 1}")
+
+
+@pytest.mark.parametrize("rows", [1, 8, 12, 130, 300])
+def test_silu_gated_feed_forward_alone(rows):
+    """The feed-forward part alone in bfloat16: few rows take the weight-streaming product
+    with the gate in its epilogue, many rows the tcgen05 product with it, the sizes between
+    the library's product and the activation kernel; all against act(gate) * up in 64-bit."""
+    from strata_inference_b200.parts.base import Runtime, build_part
+    from strata_inference_b200.parts.feed_forward import GatedMLP
+    g = torch.Generator().manual_seed(rows)
+    hidden, inter = 128, 256
+    stored = {"gate_proj.weight": torch.randn((inter, hidden), generator=g) * 0.2,
+              "up_proj.weight": torch.randn((inter, hidden), generator=g) * 0.2,
+              "down_proj.weight": torch.randn((hidden, inter), generator=g) * 0.2}
+    stored = {n: t.to(torch.bfloat16) for n, t in stored.items()}
+    rt = Runtime("cuda:0", torch.bfloat16)
+    part = build_part(GatedMLP, ({"intermediate_size": inter, "activation": "silu"}, hidden),
+                      {n: t.cuda() for n, t in stored.items()}, rt)
+    x = (torch.randn((rows, hidden), generator=g)).to(torch.bfloat16)
+    got = part.forward(x.cuda(), None).float().cpu().double()
+    p = {n.split("_")[0]: t.double() for n, t in stored.items()}
+    ref = plain.dense_ff(x.double(), p)
+    assert (got - ref).abs().max().item() <= 2e-2 * ref.abs().max().item()
