@@ -78,32 +78,46 @@ __global__ void __launch_bounds__(128) delta_prepare_kernel(DeltaPrepareArgs p) 
         }
         return;
     }
-    // the convolved, activated value of channel c of this row
-    auto channel = [&](int c) {
-        float acc = 0.f;
+    // the convolved, activated values of 8 channels c0 + lane + 32 i (those below c1): all
+    // loads of a tap are asked for before any is used
+    auto channels8 = [&](int c0, int c1, float (&y)[8]) {
+#pragma unroll
+        for (int i = 0; i < 8; ++i) y[i] = 0.f;
         for (int j = 0; j < p.taps; ++j) {
             const int at = pos - (p.taps - 1) + j;      // position of the tap's input
-            float x = 0.f;
-            if (at >= start) x = to_f32(proj[(size_t)(row0 + at - start) * p.stride + c]);
-            else if (hist) x = hist[(size_t)(at - start + p.taps - 1) * channels + c];
-            acc += p.conv_w[(size_t)c * p.taps + j] * x;
+            float x[8], w[8];
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+                const int c = c0 + lane + 32 * i;
+                x[i] = w[i] = 0.f;
+                if (c < c1) {
+                    w[i] = p.conv_w[(size_t)c * p.taps + j];
+                    if (at >= start) x[i] = to_f32(proj[(size_t)(row0 + at - start) * p.stride + c]);
+                    else if (hist) x[i] = hist[(size_t)(at - start + p.taps - 1) * channels + c];
+                }
+            }
+#pragma unroll
+            for (int i = 0; i < 8; ++i) y[i] += w[i] * x[i];
         }
-        return silu_f(acc);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) y[i] = silu_f(y[i]);
     };
+    float x[8];
     if (unit >= 2 * p.G) {                                   // a v head
         const int c0 = 2 * nqk + (unit - 2 * p.G) * p.vd;
-        for (int d = lane; d < p.vd; d += 32)
-            p.vc[(size_t)r * p.H * p.vd + (c0 - 2 * nqk) + d] = channel(c0 + d);
+        for (int d0 = 0; d0 < p.vd; d0 += 256) {
+            channels8(c0 + d0, c0 + p.vd, x);
+#pragma unroll
+            for (int i = 0; i < 8; ++i)
+                if (d0 + lane + 32 * i < p.vd)
+                    p.vc[(size_t)r * p.H * p.vd + (c0 - 2 * nqk) + d0 + lane + 32 * i] = x[i];
+        }
         return;
     }
-    float x[8];                                              // kd <= 256
+    channels8(unit * p.kd, (unit + 1) * p.kd, x);            // kd <= 256: one round
     float ss = 0.f;
 #pragma unroll
-    for (int i = 0; i < 8; ++i) {
-        const int d = lane + 32 * i;
-        x[i] = d < p.kd ? channel(unit * p.kd + d) : 0.f;
-        ss += x[i] * x[i];
-    }
+    for (int i = 0; i < 8; ++i) ss += x[i] * x[i];           // (channels beyond kd gave silu(0) = 0)
     float inv = 1.0f / sqrtf(warp_sum(ss) + 1e-6f);
     if (unit < p.G) inv *= 1.0f / sqrtf((float)p.kd);
     float* dst = (unit < p.G ? p.qn : p.kn) + (size_t)r * nqk + (size_t)(unit % p.G) * p.kd;
@@ -166,6 +180,7 @@ struct ScanArgs {
 
 constexpr int kPerLane = 16;     // rows of a column that one lane holds
 constexpr int kMaxLanes = 16;    // lanes that share a column at most
+constexpr int kScanThreads = 64;
 constexpr int kChunk = 8;        // tokens staged in shared memory at a time
 
 template <int L> __device__ __forceinline__ float lanes_sum(float v) {
@@ -176,7 +191,7 @@ template <int L> __device__ __forceinline__ float lanes_sum(float v) {
 
 __device__ __forceinline__ float log_sigmoid_f(float z) { return -softplus_f(-z); }
 
-// 64 threads = 64 / L columns, each held by L neighbouring lanes; grid (column tiles, heads,
+// kScanThreads threads = kScanThreads / L columns, each held by L neighbouring lanes; grid (column tiles, heads,
 // sequences).  Lane s of a column owns the rows ((i * L + s) * 4 .. + 3), so that
 // the lanes of a column read neighbouring 16-byte pieces of it (i = 0..kPerLane / 4 - 1).
 //
@@ -187,11 +202,13 @@ __device__ __forceinline__ float log_sigmoid_f(float z) { return -softplus_f(-z)
 // kChunk threads, in closed form: with F_t = f_1 + .. + f_t inside the chunk and m_0 the
 // maximum before it,  m_t = max(F_t + m_0, max_{s <= t} (i_s + F_t - F_s)).
 template <int MODE, typename TQ, typename TG, int L, bool VEC>
-__global__ void __launch_bounds__(64) recurrent_scan_kernel(ScanArgs p) {
+__global__ void __launch_bounds__(kScanThreads) recurrent_scan_kernel(ScanArgs p) {
     constexpr int KP = kPerLane * L;                 // key width as staged (zeros behind kd)
-    constexpr int CB = 64 / L;                       // columns of a block
+    constexpr int NT = kScanThreads;
+    constexpr int CB = NT / L;                       // columns of a block
     constexpr int BUF = kChunk * (2 * KP + CB + 4);  // q | k | v | keep | take | i | f
-    constexpr int NQ = kChunk * KP / 64, NV = kChunk * CB / 64 > 0 ? kChunk * CB / 64 : 1;
+    constexpr int NQ = kChunk * KP / NT > 0 ? kChunk * KP / NT : 1;
+    constexpr int NV = kChunk * CB / NT > 0 ? kChunk * CB / NT : 1;
     extern __shared__ __align__(16) float staged[];
     __shared__ float m_carry;
     pdl_trigger();
@@ -228,58 +245,72 @@ __global__ void __launch_bounds__(64) recurrent_scan_kernel(ScanArgs p) {
     const TQ* qp = (const TQ*)p.q + (size_t)g * p.kd;
     const TQ* kp = (const TQ*)p.k + (size_t)g * p.kd;
     const TQ* vp = (const TQ*)p.v + (size_t)h * p.vd;
-    float rq[NQ], rk[NQ], rv[NV], rg = 0.f;
+    TQ rq[NQ], rk[NQ], rv[NV];
+    TG rg = from_f32<TG>(0.f);
 
-    // the chunk's values from global memory into registers ...
+    // the chunk's values from global memory into registers, as they are stored: nothing is
+    // computed from them here, so no instruction waits for them before the chunk in hand
+    // has been worked on ...
     auto fetch = [&](int c) {
         const int t0 = c * kChunk;
 #pragma unroll
         for (int i = 0; i < NQ; ++i) {
-            const int e = tid + 64 * i, t = e / KP, d = e % KP;
-            const bool in = t0 + t < n && d < p.kd;
+            const int e = tid + NT * i, t = e / KP, d = e % KP;
+            const bool in = e < kChunk * KP && t0 + t < n && d < p.kd;
             const size_t r = (size_t)(row0 + t0 + t);
-            rq[i] = in ? to_f32(qp[r * p.q_stride + d]) * p.q_scale : 0.f;
-            rk[i] = in ? to_f32(kp[r * p.k_stride + d]) : 0.f;
+            rq[i] = from_f32<TQ>(0.f);
+            rk[i] = from_f32<TQ>(0.f);
+            if (in) {
+                rq[i] = qp[r * p.q_stride + d];
+                rk[i] = kp[r * p.k_stride + d];
+            }
         }
 #pragma unroll
         for (int i = 0; i < NV; ++i) {
-            const int e = tid + 64 * i, t = e / CB, c2 = blockIdx.x * CB + e % CB;
-            rv[i] = 0.f;
-            if (e < kChunk * CB && t0 + t < n) {
-                const size_t r = (size_t)(row0 + t0 + t);
-                if (c2 < p.vd) rv[i] = to_f32(vp[r * p.v_stride + c2]);
-                else if (MODE == SCAN_MEMORY && c2 == p.vd) rv[i] = 1.0f;
-            }
+            const int e = tid + NT * i, t = e / CB, c2 = blockIdx.x * CB + e % CB;
+            rv[i] = from_f32<TQ>(0.f);
+            if (e < kChunk * CB && t0 + t < n && c2 < p.vd)
+                rv[i] = vp[(size_t)(row0 + t0 + t) * p.v_stride + c2];
         }
         if (tid < 2 * kChunk) {
             const int t = tid % kChunk;
-            rg = 0.f;
+            rg = from_f32<TG>(0.f);
             if (t0 + t < n) {
                 const size_t r = (size_t)(row0 + t0 + t);
-                if (MODE == SCAN_DELTA) {
-                    rg = (tid < kChunk ? p.decay : p.beta)[r * p.H + h];
-                } else {
-                    const TG* src = (const TG*)(tid < kChunk ? p.gate_i : p.gate_f);
-                    const float bias = (tid < kChunk ? p.bias_i : p.bias_f)[h];
-                    rg = p.cap * tanhf((to_f32(src[r * p.gate_stride + h]) + bias) / p.cap);
-                    if (tid >= kChunk) rg = log_sigmoid_f(rg);
-                }
+                if (MODE == SCAN_DELTA)
+                    rg = ((const TG*)(tid < kChunk ? p.decay : p.beta))[r * p.H + h];
+                else
+                    rg = ((const TG*)(tid < kChunk ? p.gate_i : p.gate_f))[r * p.gate_stride + h];
             }
         }
     };
-    // ... and from the registers into a buffer
-    auto put = [&](float* buf) {
+    // ... and from the registers into a buffer, as 32-bit values: q scaled, the memory's
+    // gates capped (and the forget gate's log sigmoid taken)
+    auto put = [&](float* buf, int c) {
+        const int t0 = c * kChunk;
 #pragma unroll
-        for (int i = 0; i < NQ; ++i) {
-            buf[tid + 64 * i] = rq[i];
-            buf[kChunk * KP + tid + 64 * i] = rk[i];
+        for (int i = 0; i < NQ; ++i)
+            if (tid + NT * i < kChunk * KP) {
+                buf[tid + NT * i] = to_f32(rq[i]) * p.q_scale;
+                buf[kChunk * KP + tid + NT * i] = to_f32(rk[i]);
+            }
+#pragma unroll
+        for (int i = 0; i < NV; ++i) {
+            const int e = tid + NT * i, t = e / CB, c2 = blockIdx.x * CB + e % CB;
+            if (e < kChunk * CB)
+                buf[2 * kChunk * KP + e] =
+                    (MODE == SCAN_MEMORY && c2 == p.vd && t0 + t < n) ? 1.0f : to_f32(rv[i]);
         }
-#pragma unroll
-        for (int i = 0; i < NV; ++i)
-            if (tid + 64 * i < kChunk * CB) buf[2 * kChunk * KP + tid + 64 * i] = rv[i];
         // delta: keep = decay, take = beta; memory: the gates i and f, worked on below
-        if (tid < 2 * kChunk)
-            buf[2 * kChunk * KP + kChunk * CB + (MODE == SCAN_DELTA ? 0 : 2 * kChunk) + tid] = rg;
+        if (tid < 2 * kChunk) {
+            float v = to_f32(rg);
+            if (MODE == SCAN_MEMORY) {
+                const float bias = (tid < kChunk ? p.bias_i : p.bias_f)[h];
+                v = p.cap * tanhf((v + bias) / p.cap);
+                if (tid >= kChunk) v = log_sigmoid_f(v);
+            }
+            buf[2 * kChunk * KP + kChunk * CB + (MODE == SCAN_DELTA ? 0 : 2 * kChunk) + tid] = v;
+        }
     };
     // memory: keep and take of the chunk's tokens from its gates and the maximum so far
     auto gates = [&](float* buf, int c) {
@@ -308,7 +339,7 @@ __global__ void __launch_bounds__(64) recurrent_scan_kernel(ScanArgs p) {
 
     if (n_chunks > 0) {
         fetch(0);
-        put(staged);
+        put(staged, 0);
     }
     __syncthreads();
     if (n_chunks > 0) gates(staged, 0);
@@ -355,7 +386,7 @@ __global__ void __launch_bounds__(64) recurrent_scan_kernel(ScanArgs p) {
             if (live && s == 0)
                 p.out[((size_t)(row0 + c * kChunk + t) * p.H + h) * cols + col] = keep_t * sq1 + take * kq1;
         }
-        if (more) put(next);
+        if (more) put(next, c + 1);
         __syncthreads();
         if (more) gates(next, c + 1);
         __syncthreads();
@@ -383,11 +414,11 @@ template <int MODE, typename TQ, typename TG>
 static int launch_scan(const ScanArgs& p, int n_seqs, cudaStream_t s) {
     const int cols = MODE == SCAN_MEMORY ? p.vd + 1 : p.vd;
     const int L = p.kd <= 16 ? 1 : p.kd <= 32 ? 2 : p.kd <= 64 ? 4 : p.kd <= 128 ? 8 : 16;
-    const int threads = 64;
+    const int threads = kScanThreads;
     const dim3 grid((cols * L + threads - 1) / threads, p.H, n_seqs);
     const bool vec = p.kd % 4 == 0 && p.state_stride % 4 == 0 && ((uintptr_t)p.state % 16) == 0;
     // two buffers and the word that hands the running maximum from chunk to chunk
-    const size_t smem = (size_t)(2 * kChunk * (2 * kPerLane * L + 64 / L + 4) + 4) * sizeof(float);
+    const size_t smem = (size_t)(2 * kChunk * (2 * kPerLane * L + kScanThreads / L + 4) + 4) * sizeof(float);
 #define GO(LL)                                                                                     \
     do {                                                                                           \
         if (vec) sib_launch_chained(recurrent_scan_kernel<MODE, TQ, TG, LL, true>, grid, dim3(threads), smem, s, p); \
