@@ -34,6 +34,17 @@ class CacheError(RuntimeError):
     pass
 
 
+STATE_BUDGET = 24 << 30     # bytes of per-slot state a cache sized by default holds at most
+MIN_SLOTS = 16
+
+
+def _count(shape) -> int:
+    n = 1
+    for s in shape:
+        n *= int(s)
+    return n
+
+
 class CacheFull(CacheError):
     """No free page (or slot) is left for what a step needs."""
 
@@ -166,6 +177,13 @@ class SequenceCache:
         self.total_pages = -(-max_tokens // page_tokens)
         self.max_tokens = self.total_pages * page_tokens
         self.max_slots = max_slots or min(self.total_pages, 4096)
+        if max_slots is None:
+            # (state is held for every slot, live or not: where the caller names no number of
+            # slots, no more of them than keep the state within STATE_BUDGET bytes)
+            per_slot = sum(_count(need.state.shape) * torch.empty((), dtype=need.state.dtype).element_size()
+                           for need in needs if need is not None and need.state is not None)
+            if per_slot * self.max_slots > STATE_BUDGET:
+                self.max_slots = max(MIN_SLOTS, min(self.max_slots, STATE_BUDGET // per_slot))
         # groups of schedule entries with the same need
         by_need: Dict[KVNeed, List[int]] = {}
         for entry, need in enumerate(needs):

@@ -287,3 +287,21 @@ def test_silu_gated_feed_forward_alone(rows):
     p = {n.split("_")[0]: t.double() for n, t in stored.items()}
     ref = plain.dense_ff(x.double(), p)
     assert (got - ref).abs().max().item() <= 2e-2 * ref.abs().max().item()
+
+
+def test_command_line_generates_from_a_model_folder(tmp_path):
+    cfg = ALONE["delta_ff"]
+    w = plain.random_weights(cfg, seed=23)
+    model_dir = write_model(str(tmp_path / "model"), cfg, w)
+    prompt = prompts(cfg, [9], seed=24)[0]
+    p = subprocess.run([sys.executable, "-m", "strata_inference_b200.cli", "-m", model_dir, "--token-ids",
+                        ",".join(map(str, prompt)), "-n", "6", "--temp", "0", "--output-format", "json",
+                        "--dtype", "float32"], capture_output=True, text=True, timeout=900, cwd=ROOT)
+    assert p.returncode == 0, p.stderr[-2000:]
+    out = json.loads(p.stdout)
+    tokens = out["output_token_ids"]
+    assert len(tokens) == 6 and out["stop_reason"] == "max_tokens"
+    logits = plain_logits(cfg, w, list(prompt) + list(tokens))
+    for k, tok in enumerate(tokens):
+        row = logits[len(prompt) + k - 1]
+        assert (row.max() - row[tok]).item() <= 1e-4 * row.abs().max().item()
