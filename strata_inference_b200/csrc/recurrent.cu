@@ -181,6 +181,7 @@ struct ScanArgs {
 constexpr int kPerLane = 16;     // rows of a column that one lane holds
 constexpr int kMaxLanes = 16;    // lanes that share a column at most
 constexpr int kScanThreads = 64;
+constexpr int kColsPerThread = 1;   // independent columns a thread walks side by side (2: slower, see below)
 constexpr int kChunk = 8;        // tokens staged in shared memory at a time
 
 template <int L> __device__ __forceinline__ float lanes_sum(float v) {
@@ -191,7 +192,11 @@ template <int L> __device__ __forceinline__ float lanes_sum(float v) {
 
 __device__ __forceinline__ float log_sigmoid_f(float z) { return -softplus_f(-z); }
 
-// kScanThreads threads = kScanThreads / L columns, each held by L neighbouring lanes; grid (column tiles, heads,
+// kScanThreads threads = kScanThreads / L columns side by side, each held by L neighbouring lanes, and
+// kColsPerThread such sets per block (a thread walks its columns of all sets.  Measured at 8 heads
+// of 128 x 256 and one sequence of 2 048 tokens: two sets 840 us against 643 us with one; a warp
+// then issues more per cycle, but half as many warps leave half of the schedulers idle);
+// grid (column tiles, heads,
 // sequences).  Lane s of a column owns the rows ((i * L + s) * 4 .. + 3), so that
 // the lanes of a column read neighbouring 16-byte pieces of it (i = 0..kPerLane / 4 - 1).
 //
@@ -205,7 +210,9 @@ template <int MODE, typename TQ, typename TG, int L, bool VEC>
 __global__ void __launch_bounds__(kScanThreads) recurrent_scan_kernel(ScanArgs p) {
     constexpr int KP = kPerLane * L;                 // key width as staged (zeros behind kd)
     constexpr int NT = kScanThreads;
-    constexpr int CB = NT / L;                       // columns of a block
+    constexpr int NC = kColsPerThread;
+    constexpr int CW = NT / L;                       // columns side by side in a block
+    constexpr int CB = NC * CW;                      // columns of a block
     constexpr int BUF = kChunk * (2 * KP + CB + 4);  // q | k | v | keep | take | i | f
     constexpr int NQ = kChunk * KP / NT > 0 ? kChunk * KP / NT : 1;
     constexpr int NV = kChunk * CB / NT > 0 ? kChunk * CB / NT : 1;
@@ -214,32 +221,38 @@ __global__ void __launch_bounds__(kScanThreads) recurrent_scan_kernel(ScanArgs p
     pdl_trigger();
     const int tid = threadIdx.x;
     const int s = tid % L, cl = tid / L;
-    const int col = blockIdx.x * CB + cl;
+    const int col0 = blockIdx.x * CB + cl;         // this thread's columns: col0 + j * CW
     const int h = blockIdx.y, b = blockIdx.z;
     const int cols = MODE == SCAN_MEMORY ? p.vd + 1 : p.vd;
-    const bool live = col < cols;          // (idle lanes still take part in shuffles and barriers)
+    // (lanes without a column still take part in shuffles and barriers)
     const int g = h / (p.H / p.G);
     const int slot = p.seq_slot[b];
     const int row0 = p.seq_row0[b], n = p.seq_end[b] - p.seq_start[b];
     const int n_chunks = (n + kChunk - 1) / kChunk;
-    float S[kPerLane];
-    float* mine = slot >= 0 && live
-        ? p.state + (size_t)slot * p.state_stride + ((size_t)h * cols + col) * p.kd : nullptr;
+    float S[NC][kPerLane];
+    float* mine[NC];
+#pragma unroll
+    for (int j = 0; j < NC; ++j)
+        mine[j] = slot >= 0 && col0 + j * CW < cols
+            ? p.state + (size_t)slot * p.state_stride + ((size_t)h * cols + col0 + j * CW) * p.kd : nullptr;
     float* m_cell = MODE == SCAN_MEMORY && slot >= 0
         ? p.state + (size_t)slot * p.state_stride + (size_t)p.H * cols * p.kd + h : nullptr;
     pdl_wait();
 #pragma unroll
-    for (int i = 0; i < kPerLane / 4; ++i) {
-        const int d = (i * L + s) * 4;
-        if (VEC) {
-            float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
-            if (mine && d < p.kd) v = *reinterpret_cast<const float4*>(mine + d);
-            S[4 * i] = v.x; S[4 * i + 1] = v.y; S[4 * i + 2] = v.z; S[4 * i + 3] = v.w;
-        } else {
+    for (int j = 0; j < NC; ++j)
 #pragma unroll
-            for (int e = 0; e < 4; ++e) S[4 * i + e] = mine && d + e < p.kd ? mine[d + e] : 0.f;
+        for (int i = 0; i < kPerLane / 4; ++i) {
+            const int d = (i * L + s) * 4;
+            if (VEC) {
+                float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+                if (mine[j] && d < p.kd) v = *reinterpret_cast<const float4*>(mine[j] + d);
+                S[j][4 * i] = v.x; S[j][4 * i + 1] = v.y; S[j][4 * i + 2] = v.z; S[j][4 * i + 3] = v.w;
+            } else {
+#pragma unroll
+                for (int e = 0; e < 4; ++e)
+                    S[j][4 * i + e] = mine[j] && d + e < p.kd ? mine[j][d + e] : 0.f;
+            }
         }
-    }
     if (tid == 0) m_carry = m_cell ? *m_cell : 0.f;
 
     const TQ* qp = (const TQ*)p.q + (size_t)g * p.kd;
@@ -363,28 +376,34 @@ __global__ void __launch_bounds__(kScanThreads) recurrent_scan_kernel(ScanArgs p
                 qq[4 * i] = a.x; qq[4 * i + 1] = a.y; qq[4 * i + 2] = a.z; qq[4 * i + 3] = a.w;
                 kk[4 * i] = c4.x; kk[4 * i + 1] = c4.y; kk[4 * i + 2] = c4.z; kk[4 * i + 3] = c4.w;
             }
-            const float vj = buf[2 * kChunk * KP + t * CB + cl];
-            float sk[4] = {0.f, 0.f, 0.f, 0.f}, sq[4] = {0.f, 0.f, 0.f, 0.f}, kq[4] = {0.f, 0.f, 0.f, 0.f};
+            float kq[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
-            for (int i = 0; i < kPerLane; ++i) {
-                if (MODE == SCAN_DELTA) sk[i & 3] += S[i] * kk[i];
-                sq[i & 3] += S[i] * qq[i];
-                kq[i & 3] += kk[i] * qq[i];
-            }
-            const float sq1 = lanes_sum<L>((sq[0] + sq[1]) + (sq[2] + sq[3]));
+            for (int i = 0; i < kPerLane; ++i) kq[i & 3] += kk[i] * qq[i];
             const float kq1 = lanes_sum<L>((kq[0] + kq[1]) + (kq[2] + kq[3]));
-            const float keep_t = keep[t];
-            float take;       // S <- keep S + take k
-            if (MODE == SCAN_DELTA) {
-                const float sk1 = lanes_sum<L>((sk[0] + sk[1]) + (sk[2] + sk[3]));
-                take = keep[kChunk + t] * (vj - keep_t * sk1);
-            } else {
-                take = keep[kChunk + t] * vj;
-            }
+            const float keep_t = keep[t], beta_t = keep[kChunk + t];
 #pragma unroll
-            for (int i = 0; i < kPerLane; ++i) S[i] = keep_t * S[i] + take * kk[i];
-            if (live && s == 0)
-                p.out[((size_t)(row0 + c * kChunk + t) * p.H + h) * cols + col] = keep_t * sq1 + take * kq1;
+            for (int j = 0; j < NC; ++j) {         // (independent of one another: they overlap)
+                const float vj = buf[2 * kChunk * KP + t * CB + cl + j * CW];
+                float sk[4] = {0.f, 0.f, 0.f, 0.f}, sq[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+                for (int i = 0; i < kPerLane; ++i) {
+                    if (MODE == SCAN_DELTA) sk[i & 3] += S[j][i] * kk[i];
+                    sq[i & 3] += S[j][i] * qq[i];
+                }
+                const float sq1 = lanes_sum<L>((sq[0] + sq[1]) + (sq[2] + sq[3]));
+                float take;       // S <- keep S + take k
+                if (MODE == SCAN_DELTA) {
+                    const float sk1 = lanes_sum<L>((sk[0] + sk[1]) + (sk[2] + sk[3]));
+                    take = beta_t * (vj - keep_t * sk1);
+                } else {
+                    take = beta_t * vj;
+                }
+#pragma unroll
+                for (int i = 0; i < kPerLane; ++i) S[j][i] = keep_t * S[j][i] + take * kk[i];
+                if (s == 0 && col0 + j * CW < cols)
+                    p.out[((size_t)(row0 + c * kChunk + t) * p.H + h) * cols + col0 + j * CW] =
+                        keep_t * sq1 + take * kq1;
+            }
         }
         if (more) put(next, c + 1);
         __syncthreads();
@@ -393,17 +412,20 @@ __global__ void __launch_bounds__(kScanThreads) recurrent_scan_kernel(ScanArgs p
         if (MODE == SCAN_MEMORY && tid == 0 && more) m_carry = staged[2 * BUF];
         __syncthreads();
     }
-    if (mine) {
+#pragma unroll
+    for (int j = 0; j < NC; ++j) {
+        if (!mine[j]) continue;
 #pragma unroll
         for (int i = 0; i < kPerLane / 4; ++i) {
             const int d = (i * L + s) * 4;
             if (VEC) {
                 if (d < p.kd)
-                    *reinterpret_cast<float4*>(mine + d) = make_float4(S[4 * i], S[4 * i + 1], S[4 * i + 2], S[4 * i + 3]);
+                    *reinterpret_cast<float4*>(mine[j] + d) =
+                        make_float4(S[j][4 * i], S[j][4 * i + 1], S[j][4 * i + 2], S[j][4 * i + 3]);
             } else {
 #pragma unroll
                 for (int e = 0; e < 4; ++e)
-                    if (d + e < p.kd) mine[d + e] = S[4 * i + e];
+                    if (d + e < p.kd) mine[j][d + e] = S[j][4 * i + e];
             }
         }
     }
@@ -415,10 +437,11 @@ static int launch_scan(const ScanArgs& p, int n_seqs, cudaStream_t s) {
     const int cols = MODE == SCAN_MEMORY ? p.vd + 1 : p.vd;
     const int L = p.kd <= 16 ? 1 : p.kd <= 32 ? 2 : p.kd <= 64 ? 4 : p.kd <= 128 ? 8 : 16;
     const int threads = kScanThreads;
-    const dim3 grid((cols * L + threads - 1) / threads, p.H, n_seqs);
+    const int per_block = kColsPerThread * threads / L;       // columns of a block
+    const dim3 grid((cols + per_block - 1) / per_block, p.H, n_seqs);
     const bool vec = p.kd % 4 == 0 && p.state_stride % 4 == 0 && ((uintptr_t)p.state % 16) == 0;
     // two buffers and the word that hands the running maximum from chunk to chunk
-    const size_t smem = (size_t)(2 * kChunk * (2 * kPerLane * L + kScanThreads / L + 4) + 4) * sizeof(float);
+    const size_t smem = (size_t)(2 * kChunk * (2 * kPerLane * L + kColsPerThread * kScanThreads / L + 4) + 4) * sizeof(float);
 #define GO(LL)                                                                                     \
     do {                                                                                           \
         if (vec) sib_launch_chained(recurrent_scan_kernel<MODE, TQ, TG, LL, true>, grid, dim3(threads), smem, s, p); \
