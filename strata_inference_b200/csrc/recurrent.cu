@@ -29,7 +29,7 @@ __device__ __forceinline__ float softplus_f(float x) {
 
 // ---------------------------------------------------------------------------
 // Delta rule, step 1: per row, the short causal convolutions of q | k | v with silu, then
-// unit q (times kd^-1/2) and unit k per head, beta and the decay per head (kd <= 256).
+// unit q (times kd^-1/2) and unit k per head, beta and the decay per head (kd <= 512).
 // ---------------------------------------------------------------------------
 struct DeltaPrepareArgs {
     const void* proj;        // [rows, stride]: q (G kd) | k (G kd) | v (H vd) | gate (H vd) | b (H) | a (H)
@@ -114,16 +114,22 @@ __global__ void __launch_bounds__(128) delta_prepare_kernel(DeltaPrepareArgs p) 
         }
         return;
     }
-    channels8(unit * p.kd, (unit + 1) * p.kd, x);            // kd <= 256: one round
+    float x2[8];                                             // kd <= 512: two rounds of 256
+    channels8(unit * p.kd, (unit + 1) * p.kd, x);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) x2[i] = 0.f;
+    if (p.kd > 256) channels8(unit * p.kd + 256, (unit + 1) * p.kd, x2);
     float ss = 0.f;
 #pragma unroll
-    for (int i = 0; i < 8; ++i) ss += x[i] * x[i];           // (channels beyond kd gave silu(0) = 0)
+    for (int i = 0; i < 8; ++i) ss += x[i] * x[i] + x2[i] * x2[i];   // (channels beyond kd gave silu(0) = 0)
     float inv = 1.0f / sqrtf(warp_sum(ss) + 1e-6f);
     if (unit < p.G) inv *= 1.0f / sqrtf((float)p.kd);
     float* dst = (unit < p.G ? p.qn : p.kn) + (size_t)r * nqk + (size_t)(unit % p.G) * p.kd;
 #pragma unroll
-    for (int i = 0; i < 8; ++i)
+    for (int i = 0; i < 8; ++i) {
         if (lane + 32 * i < p.kd) dst[lane + 32 * i] = x[i] * inv;
+        if (256 + lane + 32 * i < p.kd) dst[256 + lane + 32 * i] = x2[i] * inv;
+    }
 }
 
 // The history after the step: the last taps - 1 inputs of each sequence.  One thread per
@@ -179,7 +185,7 @@ struct ScanArgs {
 };
 
 constexpr int kPerLane = 16;     // rows of a column that one lane holds
-constexpr int kMaxLanes = 16;    // lanes that share a column at most
+constexpr int kMaxLanes = 32;    // lanes that share a column at most
 constexpr int kScanThreads = 64;
 constexpr int kColsPerThread = 1;   // independent columns a thread walks side by side (2: slower, see below)
 constexpr int kChunk = 8;        // tokens staged in shared memory at a time
@@ -435,24 +441,35 @@ __global__ void __launch_bounds__(kScanThreads) recurrent_scan_kernel(ScanArgs p
 template <int MODE, typename TQ, typename TG>
 static int launch_scan(const ScanArgs& p, int n_seqs, cudaStream_t s) {
     const int cols = MODE == SCAN_MEMORY ? p.vd + 1 : p.vd;
-    const int L = p.kd <= 16 ? 1 : p.kd <= 32 ? 2 : p.kd <= 64 ? 4 : p.kd <= 128 ? 8 : 16;
+    const int L = p.kd <= 16 ? 1 : p.kd <= 32 ? 2 : p.kd <= 64 ? 4 : p.kd <= 128 ? 8 : p.kd <= 256 ? 16 : 32;
     const int threads = kScanThreads;
     const int per_block = kColsPerThread * threads / L;       // columns of a block
     const dim3 grid((cols + per_block - 1) / per_block, p.H, n_seqs);
     const bool vec = p.kd % 4 == 0 && p.state_stride % 4 == 0 && ((uintptr_t)p.state % 16) == 0;
     // two buffers and the word that hands the running maximum from chunk to chunk
     const size_t smem = (size_t)(2 * kChunk * (2 * kPerLane * L + kColsPerThread * kScanThreads / L + 4) + 4) * sizeof(float);
-#define GO(LL)                                                                                     \
-    do {                                                                                           \
-        if (vec) sib_launch_chained(recurrent_scan_kernel<MODE, TQ, TG, LL, true>, grid, dim3(threads), smem, s, p); \
-        else sib_launch_chained(recurrent_scan_kernel<MODE, TQ, TG, LL, false>, grid, dim3(threads), smem, s, p);    \
+#define GO_ONE(LL, VV)                                                                            \
+    do {                                                                                          \
+        if (smem > 48 * 1024) {                                                                   \
+            cudaError_t e = cudaFuncSetAttribute(recurrent_scan_kernel<MODE, TQ, TG, LL, VV>,     \
+                                                 cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
+            SIB_REQUIRE(e == cudaSuccess, "recurrent_scan: %s", cudaGetErrorString(e));           \
+        }                                                                                         \
+        sib_launch_chained(recurrent_scan_kernel<MODE, TQ, TG, LL, VV>, grid, dim3(threads), smem, s, p); \
+    } while (0)
+#define GO(LL)                  \
+    do {                        \
+        if (vec) GO_ONE(LL, true); \
+        else GO_ONE(LL, false); \
     } while (0)
     if (L == 1) GO(1);
     else if (L == 2) GO(2);
     else if (L == 4) GO(4);
     else if (L == 8) GO(8);
-    else GO(16);
+    else if (L == 16) GO(16);
+    else GO(32);
 #undef GO
+#undef GO_ONE
     return sib_check_launch("recurrent_scan");
 }
 

@@ -63,8 +63,8 @@ class GatedDeltaRule:
         kd, vd, taps = int(params["head_dim"]), int(params["value_dim"]), int(params["conv_taps"])
         if H <= 0 or G <= 0 or H % G:
             raise ConfigError(f"gated_delta: {H} heads cannot share {G} q/k heads")
-        if not 0 < kd <= 256 or vd <= 0 or not 1 <= taps <= 64:
-            raise ConfigError(f"gated_delta: head_dim {kd} (at most 256), value_dim {vd}, "
+        if not 0 < kd <= 512 or vd <= 0 or not 1 <= taps <= 64:
+            raise ConfigError(f"gated_delta: head_dim {kd} (at most 512), value_dim {vd}, "
                               f"{taps} taps (1 to 64)")
         return H, G, kd, vd, taps
 
@@ -148,8 +148,8 @@ class MatrixMemory:
     @staticmethod
     def _sizes(params: Mapping):
         H, kd, vd = int(params["num_heads"]), int(params["head_dim"]), int(params["value_dim"])
-        if H <= 0 or not 0 < kd <= 256 or vd <= 0:
-            raise ConfigError(f"matrix_memory: {H} heads, head_dim {kd} (at most 256), value_dim {vd}")
+        if H <= 0 or not 0 < kd <= 512 or vd <= 0:
+            raise ConfigError(f"matrix_memory: {H} heads, head_dim {kd} (at most 512), value_dim {vd}")
         return H, kd, vd
 
     @classmethod

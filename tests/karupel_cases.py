@@ -76,6 +76,13 @@ WIDE = model(128, 300, [
     delta(1, 1, 256, 32, 4),
 ])
 
+# recurrent matrices with more than 256 rows, heads of attention wider than 256
+BROAD = model(96, 150, [
+    delta(1, 1, 320, 16, 2),
+    mlstm(1, 264, 8),
+    attention(2, 1, 272, 24, scale=0.05, rot={"base": 1000.0, "dims": 100}, ff=40),
+])
+
 # attention alone with a scale that makes the softmax pick a few keys among hundreds
 SHARP = model(64, 200, [
     attention(4, 2, 32, 16, scale=1.0, rot=ROT_HALF, v_mix=True),

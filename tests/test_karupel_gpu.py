@@ -14,7 +14,7 @@ import pytest
 import torch
 
 import plain_karupel as plain
-from karupel_cases import (ALONE, MIXED, ODD, SHARP, WIDE, assert_close, plain_logits, prompts)
+from karupel_cases import (ALONE, BROAD, MIXED, ODD, SHARP, WIDE, assert_close, plain_logits, prompts)
 
 pytestmark = pytest.mark.gpu
 DTYPES = ["float32", "bfloat16"]
@@ -171,9 +171,9 @@ def test_sharp_attention_far_keys_and_page_borders():
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("name", ["odd", "wide"])
+@pytest.mark.parametrize("name", ["odd", "wide", "broad"])
 def test_other_sizes(name, dtype):
-    cfg = {"odd": ODD, "wide": WIDE}[name]
+    cfg = {"odd": ODD, "wide": WIDE, "broad": BROAD}[name]
     w = plain.random_weights(cfg, seed=16)
     eng = make_engine(cfg, w, dtype)
     a, b = prompts(cfg, [150, 37], seed=17)
