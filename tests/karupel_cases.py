@@ -76,6 +76,14 @@ WIDE = model(128, 300, [
     delta(1, 1, 256, 32, 4),
 ])
 
+# a width, heads and a vocabulary that are multiples of 2 only
+NARROW = model(100, 77, [
+    delta(2, 1, 12, 10, 3),
+    attention(2, 2, 12, 20, scale=0.3, rot={"base": 100.0, "dims": 6, "scaling": {"factor": 3.0}}, v_mix=True),
+    mlstm(2, 10, 6, cap=6.0, ff=30),
+    attention(2, 2, 18, 20, scale=0.25, v_mix=True, ff=26),
+])
+
 # recurrent matrices with more than 256 rows, heads of attention wider than 256
 BROAD = model(96, 150, [
     delta(1, 1, 320, 16, 2),

@@ -9,13 +9,13 @@ import pytest
 import torch
 
 import plain_karupel as plain
-from karupel_cases import ALONE, BROAD, MIXED, ODD, WIDE, attention, delta, mlstm, model, prompts
+from karupel_cases import ALONE, BROAD, MIXED, NARROW, ODD, WIDE, attention, delta, mlstm, model, prompts
 from strata_inference_b200.config.registry import spec_from_config
 from strata_inference_b200.config.spec import ConfigError
 from strata_inference_b200.engine.model import expected_tensors, resident_plan
 
 
-@pytest.mark.parametrize("cfg", [MIXED, ODD, WIDE, BROAD] + [ALONE[k] for k in sorted(ALONE)])
+@pytest.mark.parametrize("cfg", [MIXED, ODD, WIDE, BROAD, NARROW] + [ALONE[k] for k in sorted(ALONE)])
 def test_tensor_table_is_the_design_s(cfg):
     """The names and shapes the loader expects are the ones the plain model reads."""
     _, spec = spec_from_config(cfg)

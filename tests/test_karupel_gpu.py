@@ -14,7 +14,8 @@ import pytest
 import torch
 
 import plain_karupel as plain
-from karupel_cases import (ALONE, BROAD, MIXED, ODD, SHARP, WIDE, assert_close, plain_logits, prompts)
+from karupel_cases import (ALONE, BROAD, MIXED, NARROW, ODD, SHARP, WIDE, assert_close, plain_logits,
+                           prompts)
 
 pytestmark = pytest.mark.gpu
 DTYPES = ["float32", "bfloat16"]
@@ -81,7 +82,8 @@ def test_prompt_then_long_decoding(dtype):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("sizes", [[2, 2, 2, 2], [64, 64], [63, 2, 63], [1, 65, 3, 33], [17, 17, 17, 17, 17]])
+@pytest.mark.parametrize("sizes", [[2, 2, 2, 2], [64, 64], [63, 2, 63], [1, 65, 3, 33], [17, 17, 17, 17, 17],
+                                   [7, 8, 9, 16, 1, 15, 24]])      # (the last: around the scans' chunks of 8)
 def test_portions(sizes, dtype):
     cfg = MIXED
     w = plain.random_weights(cfg, seed=7)
@@ -154,6 +156,25 @@ def test_slots_and_pages_used_again(dtype):
     assert_close(run_whole(eng, a), ra, dtype, "a once more")
 
 
+def far_keys(cfg, w, toks):
+    """How many (row, head) pairs of the first layer's last 100 rows put more than 0.3 of their
+    weight on one key that lies more than a page (64 positions) back."""
+    m = plain.Plain(cfg, w)
+    x = m.embed[torch.tensor(toks)]
+    p, mx = plain.layer_tensors(w, 0, "mix"), cfg["layers"][0]["mixer"]
+    T, H, G, D = len(toks), mx["heads"], mx["kv_heads"], mx["dim"]
+    pos = torch.arange(T)
+    q = plain.rotate(plain.rms_unit((x @ p["q"].T + p["q.b"]).view(T, H, D), m.eps) * p["q.norm"], pos, mx["rot"])
+    k = plain.rotate(plain.rms_unit((x @ p["k"].T + p["k.b"]).view(T, G, D), m.eps) * p["k.norm"], pos, mx["rot"])
+    count = 0
+    for h in range(H):
+        s = (q[:, h] @ k[:, h // (H // G)].T) * mx["scale"]
+        s = s.masked_fill(pos[None, :] > pos[:, None], float("-inf"))
+        top, at = torch.softmax(s, -1).max(-1)
+        count += int(((pos - at > 64) & (top > 0.3) & (pos >= T - 100)).sum())
+    return count
+
+
 def test_sharp_attention_far_keys_and_page_borders():
     """With a large scale the softmax picks a few keys among hundreds, wherever they lie: a
     key that is lost, shifted by one or read from the wrong page changes the logits at once.
@@ -163,7 +184,7 @@ def test_sharp_attention_far_keys_and_page_borders():
     eng = make_engine(cfg, w, dtype)
     toks = prompts(cfg, [330], seed=15)[0]
     ref = plain_logits(cfg, w, toks)
-    # (the weights attend far back: over the last 100 rows, the heaviest key is often 100+ back)
+    assert far_keys(cfg, w, toks) > 100       # (the test is what it says: the heavy keys lie far back)
     assert_close(run_whole(eng, toks), ref, dtype, "whole prompt")
     assert_close(run_portions(eng, toks, [64, 64, 64, 64]), ref, dtype, "portions of one page")
     assert_close(run_portions(eng, toks, [63, 2, 63, 1, 1, 62, 66]), ref, dtype, "portions around page borders")
@@ -171,9 +192,9 @@ def test_sharp_attention_far_keys_and_page_borders():
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("name", ["odd", "wide", "broad"])
+@pytest.mark.parametrize("name", ["odd", "wide", "broad", "narrow"])
 def test_other_sizes(name, dtype):
-    cfg = {"odd": ODD, "wide": WIDE, "broad": BROAD}[name]
+    cfg = {"odd": ODD, "wide": WIDE, "broad": BROAD, "narrow": NARROW}[name]
     w = plain.random_weights(cfg, seed=16)
     eng = make_engine(cfg, w, dtype)
     a, b = prompts(cfg, [150, 37], seed=17)
