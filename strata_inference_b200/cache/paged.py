@@ -61,6 +61,8 @@ class KVNeed:
     head_dim: int            # width of a key
     window: int = 0          # 0: every earlier position stays visible
     value_dim: int = 0       # width of a value; 0: the same as a key
+    # a value is (the leading part of) its key's cell: no pool of values is kept
+    values_in_keys: bool = False
 
     @property
     def v_dim(self) -> int:
@@ -140,7 +142,8 @@ class KVGroup:
         # zeroed once: kernels that work on whole tiles of positions may load a
         # cell that is masked out, and its bits must at least be a number
         self.k = torch.zeros(shape + (need.head_dim,), dtype=dtype, device=device)
-        self.v = torch.zeros(shape + (need.v_dim,), dtype=dtype, device=device)
+        self.v = self.k if need.values_in_keys else \
+            torch.zeros(shape + (need.v_dim,), dtype=dtype, device=device)
         self.table_host = torch.zeros((max_slots, self.pages_per_seq), dtype=torch.int32)
         self.table = torch.zeros((max_slots, self.pages_per_seq), dtype=torch.int32, device=device)
         self.pages: List[List[int]] = [[] for _ in range(max_slots)]
@@ -161,13 +164,17 @@ class KVGroup:
         return room if start is None else max(self.ring_tokens - start, room)
 
     def bytes(self) -> int:
-        return (self.k.numel() + self.v.numel()) * self.k.element_size()
+        held = self.k.numel() + (0 if self.v is self.k else self.v.numel())
+        return held * self.k.element_size()
 
 
 class SequenceCache:
     def __init__(self, needs: Sequence[Optional[CacheNeed]], max_tokens: int, max_seq_len: int,
                  dtype: torch.dtype, device, page_tokens: int = 64,
-                 max_slots: Optional[int] = None, max_continuation: Optional[int] = None):
+                 max_slots: Optional[int] = None, max_continuation: Optional[int] = None,
+                 named_state: Optional[Dict[str, StateNeed]] = None):
+        """``named_state``: fixed-size per-slot state that belongs to no schedule entry
+        (an embedding that remembers a sequence's last token), by name."""
         if page_tokens <= 0 or max_tokens <= 0 or max_seq_len <= 0:
             raise CacheError("page_tokens, max_tokens and max_seq_len must be positive")
         device = torch.device(device)
@@ -201,6 +208,9 @@ class SequenceCache:
             if need is not None and need.state is not None:
                 self.state[entry] = torch.zeros((self.max_slots,) + tuple(need.state.shape),
                                                 dtype=need.state.dtype, device=device)
+        self.named: Dict[str, torch.Tensor] = {
+            name: torch.zeros((self.max_slots,) + tuple(need.shape), dtype=need.dtype, device=device)
+            for name, need in (named_state or {}).items()}
         self._free_slots: List[int] = list(range(self.max_slots - 1, -1, -1))
         self._live = [False] * self.max_slots
         self.lengths = [0] * self.max_slots
@@ -218,7 +228,7 @@ class SequenceCache:
             raise CacheError(f"slot {s} handed out twice")
         self._live[s] = True
         self.lengths[s] = 0
-        for t in self.state.values():
+        for t in list(self.state.values()) + list(self.named.values()):
             t[s].zero_()
         return s
 
@@ -310,6 +320,9 @@ class SequenceCache:
 
     def state_view(self, entry: int) -> torch.Tensor:
         return self.state[entry]
+
+    def named_state(self, name: str) -> torch.Tensor:
+        return self.named[name]
 
     def pages_in_use(self) -> int:
         return sum(g.n_pages - g.pool.n_free for g in self.groups)

@@ -80,6 +80,8 @@ def _register_builtin() -> None:
     register_architecture(("Gemma2ForCausalLM", "gemma2"), Gemma2Config.from_dict, gemma2_spec)
     from .karupel import KarupelConfig, karupel_spec
     register_architecture(("Karupel", "karupel"), KarupelConfig.from_dict, karupel_spec)
+    from .vavupel import VavupelConfig, vavupel_spec
+    register_architecture(("Vavupel", "vavupel"), VavupelConfig.from_dict, vavupel_spec)
 
 
 _register_builtin()

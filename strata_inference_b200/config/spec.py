@@ -64,10 +64,14 @@ class ScheduleEntry:
     """One run of a layer.  ``layer`` indexes :attr:`ModelSpec.layers` (the
     same index may appear more than once: the weights are then shared).
     ``cache_of`` names an earlier schedule entry whose keys and values (or
-    state) this run reads instead of writing its own."""
+    state) this run reads instead of writing its own.  ``begins_pass``: before this
+    run the residual stream is mixed with the embedding's output by the model's
+    ``pass_mix`` part (a model whose layers are walked several times does this at
+    the start of every pass)."""
 
     layer: int
     cache_of: Optional[int] = None
+    begins_pass: bool = False
 
 
 @dataclass(frozen=True)
@@ -85,6 +89,11 @@ class ModelSpec:
     stop_tokens: Tuple[int, ...] = ()
     # stored names for local names, per site, as in LayerSpec.tensor_names
     tensor_names: Mapping[str, Mapping[str, str]] = field(default_factory=dict)
+    # the part that runs before every schedule entry with ``begins_pass`` (a registered
+    # "joint": forward(h, x0) -> h), named by ``names["pass_mix"]``
+    pass_mix: Optional[PartSpec] = None
+    # stored tensors that a model folder may hold although nothing reads them
+    tolerated: Tuple[str, ...] = ()
 
     def validate(self) -> None:
         if self.hidden_size <= 0 or self.vocab_size <= 0 or self.max_positions <= 0:
@@ -95,6 +104,8 @@ class ModelSpec:
             if not 0 <= e.layer < len(self.layers):
                 raise ConfigError(f"schedule[{pos}] names layer {e.layer}, "
                                   f"but there are {len(self.layers)} layers")
+            if e.begins_pass and self.pass_mix is None:
+                raise ConfigError(f"schedule[{pos}] begins a pass, but the model has no 'pass_mix' part")
             if e.cache_of is not None:
                 if not 0 <= e.cache_of < pos:
                     raise ConfigError(f"schedule[{pos}].cache_of={e.cache_of} must name "

@@ -7,6 +7,11 @@
 //     s_j = scale * <q_h, k_{g,j}>;  if cap > 0: s_j = cap * tanh(s_j / cap)
 //     visible j: max(0, p - window + 1) <= j <= p   (window 0: all j <= p)
 //     o = sum_j softmax(s)_j v_{g,j}
+// With a sink (one number per query head) the softmax's denominator has one more term,
+// e^{sink_h}: a weight that belongs to no key and no value.  With `values_in_keys` a value
+// IS its key (the same cell: attention over one shared latent row per position), so the
+// key that was loaded for the score is also what is summed and nothing is read twice; the
+// caller takes the leading columns of the output that it wants.
 // Keys at positions >= seq_start[b] (this step's own rows) are read from the
 // step's packed k/v rows when those are given; earlier ones from the cache.
 // With splits > 1 each (row, head) is cut into `splits` runs of keys whose
@@ -37,6 +42,8 @@ struct AttnRowsArgs {
     int max_pages, page_tokens, ring_tokens;
     int window, splits;
     float scale, softcap;
+    const float* sink;      // [n_heads] or null
+    int values_in_keys;
 };
 
 template <typename T> struct Vec16;
@@ -167,7 +174,7 @@ __global__ void __launch_bounds__(128) attention_rows_kernel(AttnRowsArgs p) {
             for (int e = 0; e < V; ++e) acc[i][e] *= corr;
 #pragma unroll
         for (int u = 0; u < U; ++u) {
-            if (j + u < j1) {
+            if (j + u < j1 && !p.values_in_keys) {
                 const T* vp = key_ptr<T>(p, vf, vpool, j + u, start, row0, slot, g);
 #pragma unroll
                 for (int i = 0; i < NI; ++i)
@@ -190,6 +197,16 @@ __global__ void __launch_bounds__(128) attention_rows_kernel(AttnRowsArgs p) {
     }
 
     if (p.splits == 1) {
+        if (p.sink) {       // one more term of the denominator
+            const float sk = p.sink[h];
+            const float mx = fmaxf(m, sk);
+            const float corr = expf(m - mx);
+            l = l * corr + expf(sk - mx);
+#pragma unroll
+            for (int i = 0; i < NI; ++i)
+#pragma unroll
+                for (int e = 0; e < V; ++e) acc[i][e] *= corr;
+        }
         const float inv = 1.0f / l;
         T* op = (T*)p.out + (size_t)r * p.n_heads * hd + (size_t)h * hd;
 #pragma unroll
@@ -213,7 +230,8 @@ __global__ void __launch_bounds__(128) attention_rows_kernel(AttnRowsArgs p) {
 // out[r, h, :] = sum_s acc_s e^{m_s - M} / sum_s l_s e^{m_s - M}, s in split order.
 template <typename T>
 __global__ void attention_combine_kernel(const float* __restrict__ partial, T* __restrict__ out,
-                                         int splits, int head_dim, int groups) {
+                                         int splits, int head_dim, int groups,
+                                         const float* __restrict__ sink, int n_heads) {
     extern __shared__ float weight[];   // [splits] e^{m_s - M}, 0 for an empty split
     pdl_trigger();
     pdl_wait();
@@ -229,7 +247,9 @@ __global__ void attention_combine_kernel(const float* __restrict__ partial, T* _
     __syncthreads();
     float M = -INFINITY;
     for (int w = 0; w < (int)((blockDim.x + 31) >> 5); ++w) M = fmaxf(M, scratch[w]);
-    float part = 0.f;
+    const float sk = sink ? sink[unit % n_heads] : -INFINITY;
+    M = fmaxf(M, sk);
+    float part = threadIdx.x == 0 && sink ? expf(sk - M) : 0.f;
     for (int s = threadIdx.x; s < splits; s += blockDim.x) {
         const float* ps = pp + (size_t)s * (head_dim + 2);
         const float w = ps[1] > 0.f ? expf(ps[0] - M) : 0.f;
@@ -286,7 +306,8 @@ int sib_launch_attention_combine_bf16(const float* partial, void* out, int units
                                       int head_dim, cudaStream_t s) {
     const CombineShape c = combine_shape(splits, head_dim);
     sib_launch_chained(attention_combine_kernel<__nv_bfloat16>, dim3(units), dim3(c.threads), c.smem,
-                       s, partial, (__nv_bfloat16*)out, splits, head_dim, c.groups);
+                       s, partial, (__nv_bfloat16*)out, splits, head_dim, c.groups,
+                       (const float*)nullptr, 1);
     return sib_check_launch("attention_combine");
 }
 
@@ -302,7 +323,7 @@ SIB_EXPORT int sib_attention_rows(
     int ring_tokens, const int* row_pos, const int* row_seq, const int* seq_slot,
     const int* seq_start, const int* seq_row0, void* out, float* partial, int dtype, int rows,
     int n_heads, int n_kv, int head_dim, float scale, float softcap, int window, int splits,
-    void* stream) {
+    const float* sink, int values_in_keys, void* stream) {
     if (rows == 0) return 0;
     SIB_REQUIRE(rows > 0 && n_heads > 0 && n_kv > 0 && n_heads % n_kv == 0,
                 "attention_rows: rows=%d heads=%d kv_heads=%d", rows, n_heads, n_kv);
@@ -325,7 +346,8 @@ SIB_EXPORT int sib_attention_rows(
                 "attention_rows: rows must start on 16-byte boundaries");
     AttnRowsArgs p{q, k_new, v_new, k_pool, v_pool, out, partial, row_pos, row_seq, seq_slot,
                    seq_start, seq_row0, page_table, q_stride, kv_stride, rows, n_heads, n_kv,
-                   head_dim, max_pages, page_tokens, ring_tokens, window, splits, scale, softcap};
+                   head_dim, max_pages, page_tokens, ring_tokens, window, splits, scale, softcap,
+                   sink, values_in_keys};
     const long long units = (long long)rows * n_heads * splits;
     const long long blocks = (units + 3) / 4;
     SIB_REQUIRE(blocks < (1ll << 31), "attention_rows: too many rows (%d)", rows);
@@ -345,6 +367,6 @@ SIB_EXPORT int sib_attention_rows(
     const CombineShape c = combine_shape(splits, head_dim);
     SIB_DISPATCH_DTYPE(dtype, sib_launch_chained(attention_combine_kernel<T>, dim3(rows * n_heads),
                                                  dim3(c.threads), c.smem, s, partial, (T*)out,
-                                                 splits, head_dim, c.groups));
+                                                 splits, head_dim, c.groups, sink, n_heads));
     return sib_check_launch("attention_combine");
 }

@@ -150,3 +150,130 @@ SIB_EXPORT int sib_softcap(float* x, long long total, float cap, void* stream) {
     softcap_kernel<<<blocks, 256, 0, (cudaStream_t)stream>>>(x, (size_t)total, cap);
     return sib_check_launch("softcap");
 }
+
+// ---------------------------------------------------------------------------
+// Embedding with a hashed bigram table beside the token table:
+//     out[r, :] = scale * table[tok_r, :] + bigram[(prev_r * mul_prev + tok_r * mul_cur) mod buckets, :]
+// and bigram[buckets, :] (the table's last row) for a sequence's first token.  prev_r is
+// the token of the row before in the same sequence; for the first row of a step that
+// continues a sequence it is what the slot's state holds (last_token[slot]), which a second
+// small kernel brings up to the step's end afterwards.  Rows of a sequence without a slot
+// (fillers of a recorded step) store nothing.
+// Plain counterpart: tests/plain_vavupel.py bigram_embedding().
+// ---------------------------------------------------------------------------
+template <typename T>
+__global__ void bigram_embed_kernel(const int* __restrict__ tokens, const T* __restrict__ table,
+                                    const T* __restrict__ bigram, const int* __restrict__ row_pos,
+                                    const int* __restrict__ row_seq, const int* __restrict__ seq_slot,
+                                    const int* __restrict__ seq_row0, const int* __restrict__ last_token,
+                                    float* __restrict__ out, int hidden, float scale, int buckets,
+                                    long long mul_prev, long long mul_cur) {
+    pdl_trigger();
+    pdl_wait();
+    const int r = blockIdx.x;
+    const int tok = tokens[r];
+    long long pick = buckets;
+    if (row_pos[r] > 0) {
+        const int b = row_seq[r];
+        const int slot = seq_slot[b];
+        const long long prev = r > seq_row0[b] ? tokens[r - 1] : (slot >= 0 ? last_token[slot] : 0);
+        pick = (prev * mul_prev + (long long)tok * mul_cur) % buckets;
+        if (pick < 0) pick += buckets;
+    }
+    const T* src = table + (size_t)tok * hidden;
+    const T* two = bigram + (size_t)pick * hidden;
+    float* dst = out + (size_t)r * hidden;
+    for (int i = threadIdx.x; i < hidden; i += blockDim.x)
+        dst[i] = to_f32(src[i]) * scale + to_f32(two[i]);
+}
+
+__global__ void last_token_kernel(const int* __restrict__ tokens, const int* __restrict__ seq_slot,
+                                  const int* __restrict__ seq_start, const int* __restrict__ seq_end,
+                                  const int* __restrict__ seq_row0, int* __restrict__ last_token,
+                                  int n_seqs) {
+    pdl_trigger();
+    pdl_wait();
+    const int b = blockIdx.x * blockDim.x + threadIdx.x;
+    if (b >= n_seqs) return;
+    const int slot = seq_slot[b];
+    const int n = seq_end[b] - seq_start[b];
+    if (slot >= 0 && n > 0) last_token[slot] = tokens[seq_row0[b] + n - 1];
+}
+
+SIB_EXPORT int sib_bigram_embed(const int* tokens, const void* table, const void* bigram,
+                                int table_dtype, const int* row_pos, const int* row_seq,
+                                const int* seq_slot, const int* seq_start, const int* seq_end,
+                                const int* seq_row0, int* last_token, float* out, int rows,
+                                int n_seqs, int hidden, float scale, int buckets, long long mul_prev,
+                                long long mul_cur, void* stream) {
+    if (rows == 0) return 0;
+    SIB_REQUIRE(rows > 0 && n_seqs > 0 && hidden > 0 && buckets > 0,
+                "bigram_embed: rows=%d sequences=%d hidden=%d buckets=%d", rows, n_seqs, hidden, buckets);
+    SIB_REQUIRE(row_pos && row_seq && seq_slot && seq_start && seq_end && seq_row0 && last_token,
+                "bigram_embed: the step's tables and the slots' last tokens are needed");
+    cudaStream_t s = (cudaStream_t)stream;
+    SIB_DISPATCH_DTYPE(table_dtype,
+                       sib_launch_chained(bigram_embed_kernel<T>, dim3(rows), dim3(256), 0, s, tokens,
+                                          (const T*)table, (const T*)bigram, row_pos, row_seq, seq_slot,
+                                          seq_row0, (const int*)last_token, out, hidden, scale, buckets,
+                                          mul_prev, mul_cur));
+    int rc = sib_check_launch("bigram_embed");
+    if (rc) return rc;
+    sib_launch_chained(last_token_kernel, dim3((n_seqs + 127) / 128), dim3(128), 0, s, tokens, seq_slot,
+                       seq_start, seq_end, seq_row0, last_token, n_seqs);
+    return sib_check_launch("last_token");
+}
+
+// out = act(x), one value per value: the activation of a feed-forward without a gate.
+// act 2: the square of max(x, 0).
+enum { ACT_RELU_SQUARED = 2 };
+template <typename T>
+__global__ void activate_kernel(const T* __restrict__ x, T* __restrict__ out, size_t total, int act) {
+    pdl_trigger();
+    pdl_wait();
+    for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total;
+         idx += (size_t)gridDim.x * blockDim.x) {
+        const float v = to_f32(x[idx]);
+        float y;
+        if (act == ACT_RELU_SQUARED) { const float p = fmaxf(v, 0.f); y = p * p; }
+        else y = gate_act(v, act);
+        out[idx] = from_f32<T>(y);
+    }
+}
+
+SIB_EXPORT int sib_activate(const void* x, void* out, int dtype, long long total, int act, void* stream) {
+    if (total == 0) return 0;
+    SIB_REQUIRE(total > 0 && act >= 0 && act <= ACT_RELU_SQUARED, "activate: %lld values, activation %d", total, act);
+    const long long want = (total + 255) / 256;
+    const int blocks = (int)(want < 148 * 16 ? want : 148 * 16);
+    SIB_DISPATCH_DTYPE(dtype, sib_launch_chained(activate_kernel<T>, dim3(blocks), dim3(256), 0,
+                                                 (cudaStream_t)stream, (const T*)x, (T*)out, (size_t)total, act));
+    return sib_check_launch("activate");
+}
+
+// out[r, :] = [a[r, :] | b[r, :]] in out's element type: two 32-bit streams side by side
+// as the input of one product.
+template <typename T>
+__global__ void pair_rows_kernel(const float* __restrict__ a, const float* __restrict__ b,
+                                 T* __restrict__ out, int hidden, size_t total) {
+    pdl_trigger();
+    pdl_wait();
+    for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total;
+         idx += (size_t)gridDim.x * blockDim.x) {
+        const size_t r = idx / (2 * (size_t)hidden);
+        const int c = (int)(idx - r * 2 * (size_t)hidden);
+        out[idx] = from_f32<T>(c < hidden ? a[r * hidden + c] : b[r * hidden + c - hidden]);
+    }
+}
+
+SIB_EXPORT int sib_pair_rows(const float* a, const float* b, void* out, int out_dtype, int rows,
+                             int hidden, void* stream) {
+    if (rows == 0) return 0;
+    SIB_REQUIRE(rows > 0 && hidden > 0 && a && b && out, "pair_rows: rows=%d hidden=%d", rows, hidden);
+    const size_t total = (size_t)rows * hidden * 2;
+    const size_t want = (total + 255) / 256;
+    const int blocks = (int)(want < 148 * 16 ? want : 148 * 16);
+    SIB_DISPATCH_DTYPE(out_dtype, sib_launch_chained(pair_rows_kernel<T>, dim3(blocks), dim3(256), 0,
+                                                     (cudaStream_t)stream, a, b, (T*)out, hidden, total));
+    return sib_check_launch("pair_rows");
+}

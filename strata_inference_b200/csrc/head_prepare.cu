@@ -192,3 +192,135 @@ SIB_EXPORT int sib_head_gate(const void* o, const void* gate, long long gate_str
                                                  gate_stride, (T*)y, n_heads, vd, pad, total));
     return sib_check_launch("head_gate");
 }
+
+// ---------------------------------------------------------------------------
+// latent_prepare: what lies between the projections and the attention kernel of an
+// attention whose keys and values of all heads are made from ONE low-rank row per position
+// (the latent c, width `rank`) plus ONE rotated key part shared by the heads (width `rd`).
+// The scores are taken against the latent itself: with k_h = U_h c,
+//     <q_h, k_h> = <U_h^T q_h, c>,
+// so a query head becomes [U_h^T q_h | rotated part of q_h] (the product with U_h is the
+// caller's, its result `q_lat`), a position's key row becomes [c | rotated shared part], both
+// `pad` wide with zeros behind, and a value is the key row's first `rank` columns.
+//
+// Per row, in 32-bit:
+//   key unit:   c = x / sqrt(mean(x^2) + eps) * w   over x = down[:rank];   the shared part
+//               down[rank : rank + rd] rotated;  the row goes to `k_rows` and to the cache
+//   query unit: [q_lat[h, r, :] | q_h's last rd columns rotated | 0]  ->  q_rows[r, h, :]
+// Rotation: the first `rot` (<= rd) columns in neighbouring pairs (2i, 2i + 1) by the angle
+// pos * inv_freq[i].
+// Plain counterpart: tests/plain_vavupel.py latent_attention().
+// ---------------------------------------------------------------------------
+struct LatentPrepareArgs {
+    const void* proj;          // [rows, proj_stride]: query heads of (qd + rd) | down (rank + rd) | ...
+    const void* q_lat;         // [n_heads, rows, rank]
+    void* q_rows;              // [rows, n_heads * pad]
+    void* k_rows;              // [rows, pad]
+    const float* c_gain;       // [rank]
+    const float* inv_freq;     // [rot / 2] or null
+    const int* row_pos;
+    const int* row_seq;
+    const int* seq_slot;
+    const int* seq_end;
+    void* k_pool;              // [pages, 1, page_tokens, pad]; null: nothing is stored
+    const int* page_table;
+    long long proj_stride;
+    int rows, n_heads, qd, rd, rank, pad, rot;
+    int max_pages, page_tokens, ring_tokens;
+    float eps;
+};
+
+template <typename T>
+__device__ __forceinline__ float rotated_pair(const T* part, int d, int rot, const float* inv_freq,
+                                              float pos) {
+    float x = to_f32(part[d]);
+    if (d < rot) {
+        const float ang = pos * inv_freq[d >> 1];
+        const float c = cosf(ang), s = sinf(ang);
+        x = (d & 1) ? x * c + to_f32(part[d - 1]) * s : x * c - to_f32(part[d + 1]) * s;
+    }
+    return x;
+}
+
+// One warp per (row, unit): n_heads query units, then the key unit.
+template <typename T>
+__global__ void __launch_bounds__(128) latent_prepare_kernel(LatentPrepareArgs p) {
+    pdl_trigger();
+    const int lane = threadIdx.x & 31;
+    const int r = blockIdx.x;
+    const int unit = blockIdx.y * 4 + (threadIdx.x >> 5);
+    if (unit > p.n_heads) return;
+    const float pos = (float)p.row_pos[r];
+    const int rot = p.inv_freq ? p.rot : 0;
+    pdl_wait();
+    const T* row = (const T*)p.proj + (size_t)r * p.proj_stride;
+    if (unit < p.n_heads) {
+        const T* lat = (const T*)p.q_lat + ((size_t)unit * p.rows + r) * p.rank;
+        const T* part = row + (size_t)unit * (p.qd + p.rd) + p.qd;
+        T* out = (T*)p.q_rows + ((size_t)r * p.n_heads + unit) * p.pad;
+        for (int d = lane; d < p.pad; d += 32) {
+            T y = from_f32<T>(0.f);
+            if (d < p.rank) y = lat[d];
+            else if (d < p.rank + p.rd) y = from_f32<T>(rotated_pair<T>(part, d - p.rank, rot, p.inv_freq, pos));
+            out[d] = y;
+        }
+        return;
+    }
+    T* dst = nullptr;
+    if (p.k_pool) {
+        const int b = p.row_seq[r];
+        const int slot = p.seq_slot[b];
+        const int at = p.row_pos[r];
+        bool keep = slot >= 0;               // (a filling row's sequence holds no slot)
+        int cell = at;
+        if (keep && p.ring_tokens > 0) {
+            keep = at >= p.seq_end[b] - p.ring_tokens;
+            cell = at % p.ring_tokens;
+        }
+        if (keep) {
+            const int page = p.page_table[(size_t)slot * p.max_pages + cell / p.page_tokens];
+            dst = (T*)p.k_pool + ((size_t)page * p.page_tokens + cell % p.page_tokens) * p.pad;
+        }
+    }
+    const T* down = row + (size_t)p.n_heads * (p.qd + p.rd);
+    float ss = 0.f;
+    for (int d = lane; d < p.rank; d += 32) {
+        const float x = to_f32(down[d]);
+        ss += x * x;
+    }
+    const float inv = 1.0f / sqrtf(warp_sum(ss) / (float)p.rank + p.eps);
+    T* out = (T*)p.k_rows + (size_t)r * p.pad;
+    for (int d = lane; d < p.pad; d += 32) {
+        float x = 0.f;
+        if (d < p.rank) x = to_f32(down[d]) * inv * p.c_gain[d];
+        else if (d < p.rank + p.rd) x = rotated_pair<T>(down + p.rank, d - p.rank, rot, p.inv_freq, pos);
+        const T y = from_f32<T>(x);
+        out[d] = y;
+        if (dst) dst[d] = y;
+    }
+}
+
+SIB_EXPORT int sib_latent_prepare(
+    const void* proj, long long proj_stride, const void* q_lat, void* q_rows, void* k_rows, int dtype,
+    const float* c_gain, float eps, const float* inv_freq, int rot, const int* row_pos,
+    const int* row_seq, const int* seq_slot, const int* seq_end, void* k_pool, const int* page_table,
+    int max_pages, int page_tokens, int ring_tokens, int rows, int n_heads, int qd, int rd, int rank,
+    int pad, void* stream) {
+    if (rows == 0) return 0;
+    SIB_REQUIRE(rows > 0 && n_heads > 0 && qd > 0 && rd >= 0 && rank > 0 && pad >= rank + rd,
+                "latent_prepare: rows=%d heads=%d widths %d + %d, rank %d in rows of %d", rows, n_heads,
+                qd, rd, rank, pad);
+    SIB_REQUIRE(rot >= 0 && rot % 2 == 0 && rot <= rd && (rot == 0 || inv_freq != nullptr),
+                "latent_prepare: %d rotated dimensions of %d", rot, rd);
+    SIB_REQUIRE(row_pos && c_gain && q_lat && q_rows && k_rows, "latent_prepare: an argument is missing");
+    SIB_REQUIRE(k_pool == nullptr || (page_table && row_seq && seq_slot && seq_end && page_tokens > 0 &&
+                                      max_pages > 0),
+                "latent_prepare: incomplete cache description");
+    SIB_REQUIRE((n_heads + 4) / 4 < 65536, "latent_prepare: too many heads (%d)", n_heads);
+    LatentPrepareArgs p{proj, q_lat, q_rows, k_rows, c_gain, rot ? inv_freq : nullptr, row_pos, row_seq,
+                        seq_slot, seq_end, k_pool, page_table, proj_stride, rows, n_heads, qd, rd, rank,
+                        pad, rot, max_pages, page_tokens, ring_tokens, eps};
+    SIB_DISPATCH_DTYPE(dtype, sib_launch_chained(latent_prepare_kernel<T>, dim3(rows, (n_heads + 4) / 4),
+                                                 dim3(128), 0, (cudaStream_t)stream, p));
+    return sib_check_launch("latent_prepare");
+}

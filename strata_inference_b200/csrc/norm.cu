@@ -416,3 +416,83 @@ SIB_EXPORT int sib_add_rms_norm(const void* a, int dtype, const float* post_gain
     });
     return sib_check_launch("add_rms_norm");
 }
+
+// ---------------------------------------------------------------------------
+// Dynamic Tanh: a norm without statistics, element by element
+//     dyt(x) = tanh(alpha x) w + b          (alpha one number, w and b one per column)
+// alone (with a row gather) and fused with the residual add around it, as the RMS norm is:
+//     h[r, :] += post ? dyt_post(a[r, :]) : a[r, :]
+//     out[r, :] = pre ? dyt_pre(h[r, :]) : h[r, :]             (only if out)
+// Everything is 32-bit; alpha is read from the device (it is a stored tensor).
+// Plain counterpart: tests/plain_vavupel.py dynamic_tanh().
+// ---------------------------------------------------------------------------
+template <typename Tin, typename Tout>
+__global__ void dyt_norm_kernel(const Tin* __restrict__ x, const int* __restrict__ rows,
+                                const float* __restrict__ w, const float* __restrict__ b,
+                                const float* __restrict__ alpha, Tout* __restrict__ out, int hidden) {
+    pdl_trigger();
+    pdl_wait();
+    const int i = blockIdx.x;
+    const float al = *alpha;
+    const Tin* src = x + (size_t)(rows ? rows[i] : i) * hidden;
+    Tout* dst = out + (size_t)i * hidden;
+    for (int c = threadIdx.x; c < hidden; c += blockDim.x)
+        dst[c] = from_f32<Tout>(tanhf(al * to_f32(src[c])) * w[c] + b[c]);
+}
+
+template <typename T>
+__global__ void add_dyt_norm_kernel(const T* __restrict__ a, const float* __restrict__ post_w,
+                                    const float* __restrict__ post_b, const float* __restrict__ post_alpha,
+                                    float* __restrict__ h, const float* __restrict__ pre_w,
+                                    const float* __restrict__ pre_b, const float* __restrict__ pre_alpha,
+                                    T* __restrict__ out, int hidden, size_t total) {
+    pdl_trigger();
+    pdl_wait();
+    const float pa = post_w ? *post_alpha : 0.f, qa = pre_w ? *pre_alpha : 0.f;
+    for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total;
+         idx += (size_t)gridDim.x * blockDim.x) {
+        const int c = (int)(idx % hidden);
+        float y = to_f32(a[idx]);
+        if (post_w) y = tanhf(pa * y) * post_w[c] + post_b[c];
+        const float s = h[idx] + y;
+        h[idx] = s;
+        if (out) out[idx] = from_f32<T>(pre_w ? tanhf(qa * s) * pre_w[c] + pre_b[c] : s);
+    }
+}
+
+SIB_EXPORT int sib_dyt_norm(const void* x, int in_dtype, const int* rows, const float* w,
+                            const float* b, const float* alpha, void* out, int out_dtype,
+                            int n_rows, int hidden, void* stream) {
+    if (n_rows == 0) return 0;
+    SIB_REQUIRE(n_rows > 0 && hidden > 0 && w && b && alpha, "dyt_norm: rows=%d hidden=%d", n_rows, hidden);
+    const int threads = hidden >= 1024 ? 256 : 128;
+    cudaStream_t s = (cudaStream_t)stream;
+#define LAUNCH(TIN, TOUT)                                                                         \
+    sib_launch_chained(dyt_norm_kernel<TIN, TOUT>, dim3(n_rows), dim3(threads), 0, s, (const TIN*)x, \
+                       rows, w, b, alpha, (TOUT*)out, hidden)
+    if (in_dtype == SIB_F32 && out_dtype == SIB_F32) LAUNCH(float, float);
+    else if (in_dtype == SIB_F32 && out_dtype == SIB_BF16) LAUNCH(float, __nv_bfloat16);
+    else if (in_dtype == SIB_BF16 && out_dtype == SIB_BF16) LAUNCH(__nv_bfloat16, __nv_bfloat16);
+    else if (in_dtype == SIB_BF16 && out_dtype == SIB_F32) LAUNCH(__nv_bfloat16, float);
+    else SIB_REQUIRE(false, "dyt_norm: unknown element types %d -> %d", in_dtype, out_dtype);
+#undef LAUNCH
+    return sib_check_launch("dyt_norm");
+}
+
+SIB_EXPORT int sib_add_dyt_norm(const void* a, int dtype, const float* post_w, const float* post_b,
+                                const float* post_alpha, float* h, const float* pre_w,
+                                const float* pre_b, const float* pre_alpha, void* out, int n_rows,
+                                int hidden, void* stream) {
+    if (n_rows == 0) return 0;
+    SIB_REQUIRE(n_rows > 0 && hidden > 0, "add_dyt_norm: rows=%d hidden=%d", n_rows, hidden);
+    SIB_REQUIRE((post_w == nullptr || (post_b && post_alpha)) && (pre_w == nullptr || (pre_b && pre_alpha && out)),
+                "add_dyt_norm: a norm needs its weight, its bias and alpha (and the next one out)");
+    const size_t total = (size_t)n_rows * hidden;
+    const size_t want = (total + 255) / 256;
+    const int blocks = (int)(want < 148 * 16 ? want : 148 * 16);
+    SIB_DISPATCH_DTYPE(dtype, sib_launch_chained(add_dyt_norm_kernel<T>, dim3(blocks), dim3(256), 0,
+                                                 (cudaStream_t)stream, (const T*)a, post_w, post_b,
+                                                 post_alpha, h, pre_w, pre_b, pre_alpha, (T*)out,
+                                                 hidden, total));
+    return sib_check_launch("add_dyt_norm");
+}

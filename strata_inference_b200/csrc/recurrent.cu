@@ -13,6 +13,8 @@
 //   memory:  m' = max(f + m, i);  a = e^(f + m - m'),  b = e^(i - m');
 //            S_j <- a S_j + b v_j k,  o_j = a <S_j, q> + b v_j <k, q>
 //            with one more column whose v is 1: it holds n, and its output is <n, q>.
+//   retention:  S <- d S + k v^T,  o = S^T q  with one fixed decay d per head:
+//            S_j <- d S_j + v_j k,  o_j = d <S_j, q> + v_j <k, q>
 //
 // State of a slot: [heads][columns][kd] floats (a column's rows together), then for the
 // memory [heads] running maxima.  The delta rule's convolution history lies behind its
@@ -160,7 +162,7 @@ __global__ void conv_history_kernel(const T* __restrict__ proj, long long stride
 // ---------------------------------------------------------------------------
 // The recurrences.
 // ---------------------------------------------------------------------------
-enum { SCAN_DELTA = 0, SCAN_MEMORY = 1 };
+enum { SCAN_DELTA = 0, SCAN_MEMORY = 1, SCAN_RETENTION = 2 };
 
 struct ScanArgs {
     const void* q;           // row r, key head g at q + r * q_stride + g * kd
@@ -182,6 +184,7 @@ struct ScanArgs {
     long long q_stride, k_stride, v_stride, gate_stride, state_stride;
     int H, G, kd, vd;
     float q_scale, cap;
+    const float* head_decay; // retention: [H]
 };
 
 constexpr int kPerLane = 16;     // rows of a column that one lane holds
@@ -291,7 +294,7 @@ __global__ void __launch_bounds__(kScanThreads) recurrent_scan_kernel(ScanArgs p
             if (e < kChunk * CB && t0 + t < n && c2 < p.vd)
                 rv[i] = vp[(size_t)(row0 + t0 + t) * p.v_stride + c2];
         }
-        if (tid < 2 * kChunk) {
+        if (MODE != SCAN_RETENTION && tid < 2 * kChunk) {
             const int t = tid % kChunk;
             rg = from_f32<TG>(0.f);
             if (t0 + t < n) {
@@ -320,15 +323,17 @@ __global__ void __launch_bounds__(kScanThreads) recurrent_scan_kernel(ScanArgs p
                 buf[2 * kChunk * KP + e] =
                     (MODE == SCAN_MEMORY && c2 == p.vd && t0 + t < n) ? 1.0f : to_f32(rv[i]);
         }
-        // delta: keep = decay, take = beta; memory: the gates i and f, worked on below
+        // delta: keep = decay, take = beta; retention: keep = the head's decay, take = 1;
+        // memory: the gates i and f, worked on below
         if (tid < 2 * kChunk) {
             float v = to_f32(rg);
+            if (MODE == SCAN_RETENTION) v = tid < kChunk ? p.head_decay[h] : 1.0f;
             if (MODE == SCAN_MEMORY) {
                 const float bias = (tid < kChunk ? p.bias_i : p.bias_f)[h];
                 v = p.cap * tanhf((v + bias) / p.cap);
                 if (tid >= kChunk) v = log_sigmoid_f(v);
             }
-            buf[2 * kChunk * KP + kChunk * CB + (MODE == SCAN_DELTA ? 0 : 2 * kChunk) + tid] = v;
+            buf[2 * kChunk * KP + kChunk * CB + (MODE == SCAN_MEMORY ? 2 * kChunk : 0) + tid] = v;
         }
     };
     // memory: keep and take of the chunk's tokens from its gates and the maximum so far
@@ -543,11 +548,95 @@ SIB_EXPORT int sib_memory_scan(const void* proj, long long stride, int dtype, lo
 }
 
 // ---------------------------------------------------------------------------
+// Retention, step 1: per row and head, q and k rotated by the row's position on their first
+// `rot` dimensions in half-split pairs (i, i + rot/2; angle pos * inv_freq[i], taken in
+// 32-bit), k then times k_scale; v as it is.  All three leave as 32-bit rows.
+// One warp per (row, unit): the q heads, the k heads, the v heads.
+// ---------------------------------------------------------------------------
+struct RetentionPrepareArgs {
+    const void* proj;        // [rows, stride]: q (H kd) | k (H kd) | v (H vd) | ...
+    const float* inv_freq;   // [rot / 2] or null
+    const int* row_pos;
+    float* qn;               // [rows, H kd]
+    float* kn;               // [rows, H kd]
+    float* vc;               // [rows, H vd]
+    long long stride;
+    int rows, H, kd, vd, rot;
+    float k_scale;
+};
+
+template <typename T>
+__global__ void __launch_bounds__(128) retention_prepare_kernel(RetentionPrepareArgs p) {
+    pdl_trigger();
+    pdl_wait();
+    const int lane = threadIdx.x & 31;
+    const int r = blockIdx.x;
+    const int unit = blockIdx.y * 4 + (threadIdx.x >> 5);
+    if (unit >= 3 * p.H) return;
+    const T* row = (const T*)p.proj + (size_t)r * p.stride;
+    if (unit >= 2 * p.H) {
+        const int h = unit - 2 * p.H;
+        const T* src = row + (size_t)2 * p.H * p.kd + (size_t)h * p.vd;
+        float* dst = p.vc + ((size_t)r * p.H + h) * p.vd;
+        for (int d = lane; d < p.vd; d += 32) dst[d] = to_f32(src[d]);
+        return;
+    }
+    const bool is_q = unit < p.H;
+    const int h = is_q ? unit : unit - p.H;
+    const T* src = row + (size_t)unit * p.kd;
+    float* dst = (is_q ? p.qn : p.kn) + ((size_t)r * p.H + h) * p.kd;
+    const float pos = (float)p.row_pos[r];
+    const int half = p.inv_freq ? p.rot / 2 : 0;
+    const float post = is_q ? 1.0f : p.k_scale;
+    for (int d = lane; d < p.kd; d += 32) {
+        float x = to_f32(src[d]);
+        if (d < 2 * half) {
+            const int i = d < half ? d : d - half;
+            const float ang = pos * p.inv_freq[i];
+            const float c = cosf(ang), s = sinf(ang);
+            x = d < half ? x * c - to_f32(src[d + half]) * s : x * c + to_f32(src[d - half]) * s;
+        }
+        dst[d] = x * post;
+    }
+}
+
+SIB_EXPORT int sib_retention_prepare(const void* proj, long long stride, int dtype,
+                                     const float* inv_freq, int rot, const int* row_pos, float* qn,
+                                     float* kn, float* vc, int rows, int H, int kd, int vd,
+                                     float k_scale, void* stream) {
+    if (rows == 0) return 0;
+    SIB_REQUIRE(rows > 0 && H > 0 && kd > 0 && vd > 0 && row_pos, "retention_prepare: rows=%d heads=%d widths %d, %d",
+                rows, H, kd, vd);
+    SIB_REQUIRE(rot >= 0 && rot % 2 == 0 && rot <= kd && (rot == 0 || inv_freq != nullptr),
+                "retention_prepare: %d rotated dimensions of %d", rot, kd);
+    SIB_REQUIRE((3 * H + 3) / 4 < 65536, "retention_prepare: too many heads (%d)", H);
+    RetentionPrepareArgs p{proj, rot ? inv_freq : nullptr, row_pos, qn, kn, vc, stride, rows, H, kd, vd, rot, k_scale};
+    SIB_DISPATCH_DTYPE(dtype, sib_launch_chained(retention_prepare_kernel<T>, dim3(rows, (3 * H + 3) / 4),
+                                                 dim3(128), 0, (cudaStream_t)stream, p));
+    return sib_check_launch("retention_prepare");
+}
+
+// The retention recurrence over prepared 32-bit rows; decay: one value per head.
+SIB_EXPORT int sib_retention_scan(const float* qn, const float* kn, const float* vc,
+                                  const float* head_decay, float* state, long long state_stride,
+                                  float* out, const int* seq_slot, const int* seq_start,
+                                  const int* seq_end, const int* seq_row0, int rows, int n_seqs,
+                                  int H, int kd, int vd, void* stream) {
+    if (rows == 0) return 0;
+    if (check_scan("retention_scan", rows, n_seqs, H, H, kd, vd)) return -1;
+    SIB_REQUIRE(head_decay != nullptr, "retention_scan: the heads' decays are needed");
+    ScanArgs p{qn, kn, vc, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, state, out, nullptr,
+               seq_slot, seq_start, seq_end, seq_row0, (long long)H * kd, (long long)H * kd,
+               (long long)H * vd, 0, state_stride, H, H, kd, vd, 1.0f, 0.f, head_decay};
+    return launch_scan<SCAN_RETENTION, float, float>(p, n_seqs, (cudaStream_t)stream);
+}
+
+// ---------------------------------------------------------------------------
 // After either recurrence: each head's output divided by its root mean square, times a
 // weight, times an activated gate.
 //   x = o[r, h, :vd]            (memory: divided by max(|o[r, h, vd]|, e^-m[r, h]) + 1e-6)
 //   y[r, h, :] = x / sqrt(mean(x^2) + eps) * w[h * w_stride + :] * act(gate[r, h * vd + :])
-// act: 0 silu, 1 sigmoid.  One warp per (row, head).
+// act: 0 silu, 1 sigmoid; w null: no weight.  One warp per (row, head).
 // ---------------------------------------------------------------------------
 template <typename T>
 __global__ void __launch_bounds__(128)
@@ -573,7 +662,7 @@ head_norm_gate_kernel(const float* __restrict__ o, const float* __restrict__ m, 
     for (int e = lane; e < vd; e += 32) {
         const float z = to_f32(gate[r * gate_stride + (size_t)h * vd + e]);
         const float a = act == 0 ? silu_f(z) : sigmoid_f(z);
-        y[(size_t)unit * vd + e] = from_f32<T>(x[e] * inv * w[(size_t)h * w_stride + e] * a);
+        y[(size_t)unit * vd + e] = from_f32<T>(x[e] * inv * (w ? w[(size_t)h * w_stride + e] : 1.0f) * a);
     }
 }
 

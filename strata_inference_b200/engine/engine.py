@@ -66,7 +66,7 @@ class Engine:
         self.max_seq_len = min(max_seq_len or spec.max_positions, spec.max_positions)
         self.cache = SequenceCache(self.model.cache_needs(), max_tokens, self.max_seq_len,
                                    self.dtype, self.device, page_tokens, max_slots,
-                                   max_continuation)
+                                   max_continuation, named_state=self.model.named_state())
         self.vocab_size = spec.vocab_size
         # one xorshift64 state per slot, for the sampling kernel
         self.rng_state = torch.ones(self.cache.max_slots, dtype=torch.int64, device=self.device)

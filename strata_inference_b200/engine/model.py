@@ -11,7 +11,8 @@ from typing import Dict, List, Mapping, Optional, Tuple
 
 import torch
 
-from ..cache.paged import CacheNeed
+from ..cache.paged import CacheNeed, StateNeed
+from ..kernels import native
 from ..config.spec import ModelSpec, PartSpec
 from ..parts import registry as parts
 from ..weights.arena import DictSource, Piece, Resident, WeightArena, resident_of
@@ -28,6 +29,8 @@ def expected_tensors(spec: ModelSpec) -> Dict[str, TensorDecl]:
     for prefix, cls, args, stored in _sites(spec):
         for name, d in cls.tensors(*args).items():
             out[prefix + stored.get(name, name)] = d
+    for name in spec.tolerated:
+        out.setdefault(name, TensorDecl(None, optional=True))
     return out
 
 
@@ -47,6 +50,9 @@ def _sites(spec: ModelSpec):
         for site, norm in layer.norms.items():
             yield (layer.prefix + layer.names[site], parts.part_class("norm", norm.kind),
                    (norm.params, H), layer.tensor_names.get(site, {}))
+    if spec.pass_mix is not None:
+        yield (spec.names["pass_mix"], parts.part_class("joint", spec.pass_mix.kind),
+               (spec.pass_mix.params, H), spec.tensor_names.get("pass_mix", {}))
     yield (spec.names["final_norm"], parts.part_class("norm", spec.final_norm.kind),
            (spec.final_norm.params, H), spec.tensor_names.get("final_norm", {}))
     yield (spec.names["head"], parts.part_class("head", spec.head.kind), (spec.head.params, H, V),
@@ -113,10 +119,19 @@ class DecoderModel:
                 n.params, H, _sub(weights, layer.prefix + layer.names[site]), rt)
                 for site, n in layer.norms.items()}
             self.blocks.append(parts.part_class("block", layer.block)(mixer, ff, norms, rt))
+        self.pass_mix = None
+        if spec.pass_mix is not None:
+            self.pass_mix = parts.part_class("joint", spec.pass_mix.kind)(
+                spec.pass_mix.params, H, _sub(weights, spec.names["pass_mix"]), rt)
         self.final_norm = parts.part_class("norm", spec.final_norm.kind)(
             spec.final_norm.params, H, _sub(weights, spec.names["final_norm"]), rt)
         self.head = parts.part_class("head", spec.head.kind)(
             spec.head.params, H, V, _sub(weights, spec.names["head"]), rt, self.embedding)
+
+    def named_state(self) -> Dict[str, "StateNeed"]:
+        """Per-slot state that belongs to no schedule entry (the embedding's), by name."""
+        need = getattr(self.embedding, "state_need", None)
+        return {"embedding": need()} if need is not None else {}
 
     def cache_needs(self) -> List[Optional[CacheNeed]]:
         """One entry per schedule position; None where the run borrows a cache."""
@@ -133,6 +148,7 @@ class DecoderModel:
         # (a run that reads another run's cache reads it by slot, for every row: the rows that
         # fill a recorded step up have none)
         return (getattr(self.embedding, "captures_prompts", False)
+                and (self.pass_mix is None or getattr(self.pass_mix, "captures_prompts", False))
                 and all(getattr(b, "captures_prompts", False) for b in self.blocks)
                 and all(e.cache_of is None for e in self.spec.schedule))
 
@@ -150,10 +166,20 @@ class DecoderModel:
         from ..parts.base import chain_suspended
         h = self.embedding.forward(ctx)
         schedule = self.spec.schedule
+        x0 = None
+        if self.pass_mix is not None:
+            # (the blocks add to h in place: the embedding's output is kept beside it)
+            x0 = native.cast_rows(h, torch.empty_like(h))
         normed = None
         for pos, e in enumerate(schedule):
             block = self.blocks[e.layer]
-            nxt = self.blocks[schedule[pos + 1].layer].first_norm if pos + 1 < len(schedule) else None
+            if e.begins_pass:
+                self.rt.flush()
+                h = self.pass_mix.forward(h, x0)
+                normed = None
+            # (a run that begins a pass norms the mixed stream itself)
+            last = pos + 1 == len(schedule) or schedule[pos + 1].begins_pass
+            nxt = None if last else self.blocks[schedule[pos + 1].layer].first_norm
             cache_entry = pos if e.cache_of is None else e.cache_of
             if self.rt.chain is not None and not getattr(block, "chain_safe", False):
                 with chain_suspended(self.rt):

@@ -23,6 +23,7 @@ EPI_SWIGLU = 4          # the gated epilogue with SiLU (weight-streaming and pai
 GATED_EPILOGUES = (EPI_GEGLU, EPI_SWIGLU)
 ROPE_HALF_SPLIT, ROPE_INTERLEAVED = 0, 1
 ACT_GELU_TANH, ACT_SILU = 0, 1          # of the gated feed-forward
+ACT_RELU_SQUARED = 2                    # of the feed-forward without a gate (activate)
 GATE_SILU, GATE_SIGMOID = 0, 1          # of head_norm_gate
 
 _lib = None
@@ -372,6 +373,105 @@ def add_rms_norm(a: torch.Tensor, post_gain: Optional[torch.Tensor], post_eps: f
                                       c_int(rows), c_int(hidden), _stream()))
 
 
+@_timed(lambda x, w, b, alpha, out, rows=None: (
+    "dyt_norm", out.shape[0] * x.shape[1] * x.element_size() + _nbytes(out), 0))
+def dyt_norm(x: torch.Tensor, w: torch.Tensor, b: torch.Tensor, alpha: torch.Tensor,
+             out: torch.Tensor, rows: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """out[i] = tanh(alpha x[rows[i] if rows else i]) * w + b, element by element in 32-bit;
+    ``alpha`` is one 32-bit value on the device."""
+    _want(x, x.dtype, "x")
+    _want(out, out.dtype, "out")
+    n, hidden = out.shape
+    _f32(w, hidden, "w")
+    _f32(b, hidden, "b")
+    _f32(alpha, 1, "alpha")
+    if x.shape[1] != hidden:
+        raise KernelError("dyt_norm: shapes do not fit")
+    if rows is not None:
+        _want(rows, torch.int32, "rows")
+        if rows.numel() != n:
+            raise KernelError("dyt_norm: one row index per output row")
+    elif x.shape[0] != n:
+        raise KernelError("dyt_norm: x and out differ in rows")
+    _check(library().sib_dyt_norm(_ptr(x), _code(x.dtype), _ptr(rows), _ptr(w), _ptr(b), _ptr(alpha),
+                                  _ptr(out), _code(out.dtype), c_int(n), c_int(hidden), _stream()))
+    return out
+
+
+@_timed(lambda a, post, h, pre, out: ("add_dyt_norm", _nbytes(a, out) + 2 * _nbytes(h), 0))
+def add_dyt_norm(a: torch.Tensor, post, h: torch.Tensor, pre, out: Optional[torch.Tensor]) -> None:
+    """h += dyt_post(a) (or a when ``post`` is None); out = dyt_pre(h) (or h as activations
+    when ``pre`` is None and out is given).  ``post`` and ``pre``: (w, b, alpha) of a Dynamic
+    Tanh, 32-bit on the device."""
+    _want(h, torch.float32, "h")
+    _want(a, a.dtype, "a")
+    rows, hidden = h.shape
+    if tuple(a.shape) != (rows, hidden):
+        raise KernelError("add_dyt_norm: a and h differ in shape")
+    for triple, nm in ((post, "post"), (pre, "pre")):
+        if triple is not None:
+            _f32(triple[0], hidden, nm + " weight")
+            _f32(triple[1], hidden, nm + " bias")
+            _f32(triple[2], 1, nm + " alpha")
+    if out is not None:
+        _want(out, a.dtype, "out")
+        if tuple(out.shape) != (rows, hidden):
+            raise KernelError("add_dyt_norm: out and h differ in shape")
+    elif pre is not None:
+        raise KernelError("add_dyt_norm: the next norm needs out")
+    pw, pb, pa = post if post is not None else (None, None, None)
+    qw, qb, qa = pre if pre is not None else (None, None, None)
+    _check(library().sib_add_dyt_norm(_ptr(a), _code(a.dtype), _ptr(pw), _ptr(pb), _ptr(pa), _ptr(h),
+                                      _ptr(qw), _ptr(qb), _ptr(qa), _ptr(out), c_int(rows),
+                                      c_int(hidden), _stream()))
+
+
+@_timed(lambda ctx, table, bigram, last_token, out, *a: ("bigram_embed", 3 * _nbytes(out), 0))
+def bigram_embed(ctx, table: torch.Tensor, bigram: torch.Tensor, last_token: torch.Tensor,
+                 out: torch.Tensor, scale: float, buckets: int, mul_prev: int, mul_cur: int) -> torch.Tensor:
+    """out[r] = scale * table[token] + bigram[(previous * mul_prev + token * mul_cur) mod
+    buckets] (row ``buckets`` at a sequence's first position), 32-bit; then
+    ``last_token[slot]`` (int32, one per slot) becomes each sequence's last token of the step."""
+    _want(out, torch.float32, "out")
+    _want(last_token, torch.int32, "last_token")
+    rows, hidden = out.shape
+    if (ctx.tokens.numel() != rows or table.shape[1] != hidden or tuple(bigram.shape) != (buckets + 1, hidden)
+            or not table.is_contiguous() or not bigram.is_contiguous() or table.dtype != bigram.dtype):
+        raise KernelError("bigram_embed: shapes do not fit")
+    _check(library().sib_bigram_embed(
+        _ptr(ctx.tokens), _ptr(table), _ptr(bigram), _code(table.dtype), _ptr(ctx.row_pos),
+        _ptr(ctx.row_seq), _ptr(ctx.seq_slot), _ptr(ctx.seq_start), _ptr(ctx.seq_end),
+        _ptr(ctx.seq_row0), _ptr(last_token), _ptr(out), c_int(rows), c_int(ctx.n_seqs), c_int(hidden),
+        c_float(scale), c_int(buckets), c_longlong(mul_prev), c_longlong(mul_cur), _stream()))
+    return out
+
+
+@_timed(lambda x, out, act: ("activate", _nbytes(x, out), 0))
+def activate(x: torch.Tensor, out: torch.Tensor, act: int) -> torch.Tensor:
+    """out = act(x) value by value (ACT_RELU_SQUARED: max(x, 0) squared)."""
+    _want(x, out.dtype, "x")
+    _want(out, out.dtype, "out")
+    if x.numel() != out.numel():
+        raise KernelError("activate: x and out differ in size")
+    _check(library().sib_activate(_ptr(x), _ptr(out), _code(out.dtype), c_longlong(x.numel()),
+                                  c_int(act), _stream()))
+    return out
+
+
+@_timed(lambda a, b, out: ("pair_rows", _nbytes(a, b, out), 0))
+def pair_rows(a: torch.Tensor, b: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
+    """out[r] = [a[r] | b[r]] in out's element type; a and b are 32-bit ``[rows, hidden]``."""
+    _want(a, torch.float32, "a")
+    _want(b, torch.float32, "b")
+    _want(out, out.dtype, "out")
+    rows, hidden = a.shape
+    if tuple(b.shape) != (rows, hidden) or tuple(out.shape) != (rows, 2 * hidden):
+        raise KernelError("pair_rows: shapes do not fit")
+    _check(library().sib_pair_rows(_ptr(a), _ptr(b), _ptr(out), _code(out.dtype), c_int(rows),
+                                   c_int(hidden), _stream()))
+    return out
+
+
 @_timed(lambda qkv, *a, **kw: ("rope_store", 2 * _nbytes(qkv), 0))
 def rope_store(qkv: torch.Tensor, row_pos, row_seq, seq_slot, seq_end,
                inv_freq: Optional[torch.Tensor], rotary_dim: int, style: int,
@@ -478,6 +578,43 @@ def head_gate(o: torch.Tensor, gate: Optional[torch.Tensor], y: torch.Tensor, n_
     return y
 
 
+@_timed(lambda proj, q_lat, q_rows, k_rows, *a, **kw: ("latent_prepare", _nbytes(q_lat, q_rows, k_rows) * 2, 0))
+def latent_prepare(proj: torch.Tensor, q_lat: torch.Tensor, q_rows: torch.Tensor, k_rows: torch.Tensor,
+                   c_gain: torch.Tensor, eps: float, inv_freq: Optional[torch.Tensor], rot: int, ctx,
+                   k_pool: Optional[torch.Tensor], page_table: Optional[torch.Tensor],
+                   page_tokens: int, ring_tokens: int, n_heads: int, q_dim: int, rot_dim: int,
+                   rank: int, pad: int) -> None:
+    """Between the projections and the attention over a shared latent (csrc/head_prepare.cu):
+    ``proj`` rows hold the query heads (``q_dim`` + ``rot_dim`` each) and then the down
+    projection (``rank`` + ``rot_dim``); ``q_lat`` ``[heads, rows, rank]`` are the queries
+    already multiplied into the latent's space.  Writes ``q_rows`` ``[rows, heads * pad]``,
+    ``k_rows`` ``[rows, pad]`` and the cache cells of the rows."""
+    rows = proj.shape[0]
+    _want(proj, proj.dtype, "proj", contiguous=False)
+    for t, shape, nm in ((q_lat, (n_heads, rows, rank), "q_lat"), (q_rows, (rows, n_heads * pad), "q_rows"),
+                         (k_rows, (rows, pad), "k_rows")):
+        _want(t, proj.dtype, nm)
+        if tuple(t.shape) != shape:
+            raise KernelError(f"latent_prepare: {nm} must be {shape}")
+    if proj.stride(1) != 1 or proj.shape[1] < n_heads * (q_dim + rot_dim) + rank + rot_dim:
+        raise KernelError("latent_prepare: a projected row must hold the query heads and the down projection")
+    _f32(c_gain, rank, "c_gain")
+    if rot:
+        _f32(inv_freq, rot // 2, "inv_freq")
+    max_pages = 0
+    if k_pool is not None:
+        _want(k_pool, proj.dtype, "k_pool")
+        if tuple(k_pool.shape[1:]) != (1, page_tokens, pad) or page_table is None:
+            raise KernelError("latent_prepare: pool layout must be [pages, 1, page_tokens, pad]")
+        max_pages = page_table.shape[1]
+    _check(library().sib_latent_prepare(
+        _ptr(proj), c_longlong(proj.stride(0)), _ptr(q_lat), _ptr(q_rows), _ptr(k_rows),
+        _code(proj.dtype), _ptr(c_gain), c_float(eps), _ptr(inv_freq if rot else None), c_int(rot),
+        _ptr(ctx.row_pos), _ptr(ctx.row_seq), _ptr(ctx.seq_slot), _ptr(ctx.seq_end), _ptr(k_pool),
+        _ptr(page_table), c_int(max_pages), c_int(page_tokens), c_int(ring_tokens), c_int(rows),
+        c_int(n_heads), c_int(q_dim), c_int(rot_dim), c_int(rank), c_int(pad), _stream()))
+
+
 def _f32(t: Optional[torch.Tensor], n: int, name: str) -> None:
     if t is None:
         raise KernelError(f"{name} is needed")
@@ -577,31 +714,79 @@ def memory_scan(proj: torch.Tensor, bias_i: torch.Tensor, bias_f: torch.Tensor, 
     return out
 
 
+@_timed(lambda proj, inv_freq, rot, row_pos, qn, kn, vc, *a: (
+    "retention_prepare", proj.shape[0] * (qn.shape[1] * 2 + vc.shape[1]) * proj.element_size()
+    + _nbytes(qn, kn, vc), 0))
+def retention_prepare(proj: torch.Tensor, inv_freq: Optional[torch.Tensor], rot: int, row_pos,
+                      qn: torch.Tensor, kn: torch.Tensor, vc: torch.Tensor, n_heads: int,
+                      key_dim: int, value_dim: int, k_scale: float) -> None:
+    """From projected rows ``[q | k | v | ...]``: q and k rotated on their first ``rot``
+    dimensions (half-split pairs), k times ``k_scale``, v as it is; all 32-bit."""
+    rows = proj.shape[0]
+    _want(proj, proj.dtype, "proj", contiguous=False)
+    if proj.stride(1) != 1 or proj.shape[1] < n_heads * (2 * key_dim + value_dim):
+        raise KernelError("retention_prepare: a projected row must hold q, k and v")
+    for t, n, nm in ((qn, rows * n_heads * key_dim, "qn"), (kn, rows * n_heads * key_dim, "kn"),
+                     (vc, rows * n_heads * value_dim, "vc")):
+        _f32(t, n, nm)
+    if rot:
+        _f32(inv_freq, rot // 2, "inv_freq")
+    _check(library().sib_retention_prepare(
+        _ptr(proj), c_longlong(proj.stride(0)), _code(proj.dtype), _ptr(inv_freq if rot else None),
+        c_int(rot), _ptr(row_pos), _ptr(qn), _ptr(kn), _ptr(vc), c_int(rows), c_int(n_heads),
+        c_int(key_dim), c_int(value_dim), c_float(k_scale), _stream()))
+
+
+@_timed(lambda qn, kn, vc, decay, state, out, ctx, n_heads, key_dim, value_dim: _scan_work(
+    "retention_scan", out.shape[0], ctx.n_seqs, n_heads, key_dim, value_dim))
+def retention_scan(qn: torch.Tensor, kn: torch.Tensor, vc: torch.Tensor, decay: torch.Tensor,
+                   state: torch.Tensor, out: torch.Tensor, ctx, n_heads: int, key_dim: int,
+                   value_dim: int) -> torch.Tensor:
+    """S <- decay_h S + k v^T, o = S^T q over the step's rows, sequence by sequence, from and
+    into the slots' matrices ``state[slot, :heads * value_dim * key_dim]``; ``out`` 32-bit
+    ``[rows, heads * value_dim]``; ``decay`` one 32-bit value per head."""
+    rows = out.shape[0]
+    _want(state, torch.float32, "state")
+    _f32(qn, rows * n_heads * key_dim, "qn")
+    _f32(kn, rows * n_heads * key_dim, "kn")
+    _f32(vc, rows * n_heads * value_dim, "vc")
+    _f32(decay, n_heads, "decay")
+    _f32(out, rows * n_heads * value_dim, "out")
+    if state.shape[1] < n_heads * value_dim * key_dim:
+        raise KernelError("retention_scan: the state is too small for the matrices")
+    _check(library().sib_retention_scan(
+        _ptr(qn), _ptr(kn), _ptr(vc), _ptr(decay), _ptr(state), c_longlong(state.stride(0)),
+        _ptr(out), _ptr(ctx.seq_slot), _ptr(ctx.seq_start), _ptr(ctx.seq_end), _ptr(ctx.seq_row0),
+        c_int(rows), c_int(ctx.n_seqs), c_int(n_heads), c_int(key_dim), c_int(value_dim), _stream()))
+    return out
+
+
 @_timed(lambda o, m, w, gate, y, *a: ("head_norm_gate", _nbytes(o, y) + _nbytes(y), 0))  # (+ the gates)
-def head_norm_gate(o: torch.Tensor, m: Optional[torch.Tensor], w: torch.Tensor,
+def head_norm_gate(o: torch.Tensor, m: Optional[torch.Tensor], w: Optional[torch.Tensor],
                    gate: torch.Tensor, y: torch.Tensor, n_heads: int, value_dim: int, eps: float,
                    act: int) -> torch.Tensor:
     """y[r, h, :] = x / rms(x) * w * act(gate[r, h, :]) with x the head's 32-bit output
     (``o`` ``[rows, heads * cols]``, the first ``value_dim`` columns of a head; with ``m``
     divided by max(|column value_dim|, e^-m) + 1e-6 first).  ``w``: one weight per column
-    shared by the heads, or one per head and column.  ``gate``: a view ``[rows, heads *
+    shared by the heads, or one per head and column, or None for none.  ``gate``: a view ``[rows, heads *
     value_dim]``.  act: GATE_SILU or GATE_SIGMOID."""
     rows = y.shape[0]
     _want(o, torch.float32, "o")
     _want(y, y.dtype, "y")
-    _want(w, torch.float32, "w")
+    if w is not None:
+        _want(w, torch.float32, "w")
     _want(gate, y.dtype, "gate", contiguous=False)
     cols = o.shape[1] // n_heads
     if tuple(y.shape) != (rows, n_heads * value_dim) or o.shape[0] != rows or cols < value_dim:
         raise KernelError("head_norm_gate: shapes do not fit the head counts")
-    if w.numel() not in (value_dim, n_heads * value_dim):
+    if w is not None and w.numel() not in (value_dim, n_heads * value_dim):
         raise KernelError("head_norm_gate: the weight is per column or per head and column")
     if tuple(gate.shape) != (rows, n_heads * value_dim) or gate.stride(1) != 1:
         raise KernelError("head_norm_gate: one gate value per output")
     if m is not None:
         _f32(m, rows * n_heads, "m")
     _check(library().sib_head_norm_gate(
-        _ptr(o), _ptr(m), _ptr(w), c_int(0 if w.numel() == value_dim else value_dim), _ptr(gate),
+        _ptr(o), _ptr(m), _ptr(w), c_int(0 if w is None or w.numel() == value_dim else value_dim), _ptr(gate),
         c_longlong(gate.stride(0)), _ptr(y), _code(y.dtype), c_int(rows), c_int(n_heads),
         c_int(value_dim), c_int(cols), c_float(eps), c_int(act), _stream()))
     return y
@@ -614,7 +799,7 @@ def attention_rows_scratch_bytes(rows: int, n_heads: int, head_dim: int, splits:
 
 @_timed(lambda q, q_stride, k_new, v_new, kv_stride, k_pool, v_pool, page_table, page_tokens,
         ring_tokens, row_pos, row_seq, seq_slot, seq_start, seq_row0, out, scratch, n_heads, n_kv,
-        head_dim, scale, softcap, window, splits: (
+        head_dim, scale, softcap, window, splits, sink=None, values_in_keys=False: (
             _attention_cache_work("attention_rows (cache)", row_pos, k_pool, n_heads, head_dim,
                                   window, out.shape[0]) if k_pool is not None else
             ("attention_rows (prompt)", 2 * _nbytes(out) * (1 + 2 * n_kv / n_heads),
@@ -625,8 +810,11 @@ def attention_rows(q: torch.Tensor, q_stride: int, k_new: Optional[torch.Tensor]
                    page_table: Optional[torch.Tensor], page_tokens: int, ring_tokens: int,
                    row_pos, row_seq, seq_slot, seq_start, seq_row0, out: torch.Tensor,
                    scratch: Optional[torch.Tensor], n_heads: int, n_kv: int, head_dim: int,
-                   scale: float, softcap: float, window: int, splits: int) -> torch.Tensor:
-    """General attention of independent rows (see csrc/attention_rows.cu).
+                   scale: float, softcap: float, window: int, splits: int,
+                   sink: Optional[torch.Tensor] = None, values_in_keys: bool = False) -> torch.Tensor:
+    """General attention of independent rows (see csrc/attention_rows.cu).  ``sink``: one
+    32-bit value per query head whose exponential joins the softmax's denominator.
+    ``values_in_keys``: a value is its key's cell (``v_new`` / ``v_pool`` are not read).
 
     ``q``, ``k_new``, ``v_new`` may be views into one packed buffer; only
     their first elements' addresses and the strides are used."""
@@ -641,12 +829,15 @@ def attention_rows(q: torch.Tensor, q_stride: int, k_new: Optional[torch.Tensor]
         need = attention_rows_scratch_bytes(rows, n_heads, head_dim, splits)
         if scratch is None or scratch.numel() * scratch.element_size() < need:
             raise KernelError(f"attention_rows: {need} bytes of scratch memory are needed")
+    if sink is not None:
+        _f32(sink, n_heads, "sink")
     _check(library().sib_attention_rows(
         _ptr(q), c_int(q_stride), _ptr(k_new), _ptr(v_new), c_int(kv_stride), _ptr(k_pool),
         _ptr(v_pool), _ptr(page_table), c_int(max_pages), c_int(page_tokens), c_int(ring_tokens),
         _ptr(row_pos), _ptr(row_seq), _ptr(seq_slot), _ptr(seq_start), _ptr(seq_row0), _ptr(out),
         _ptr(scratch), _code(out.dtype), c_int(rows), c_int(n_heads), c_int(n_kv), c_int(head_dim),
-        c_float(scale), c_float(softcap), c_int(window), c_int(splits), _stream()))
+        c_float(scale), c_float(softcap), c_int(window), c_int(splits), _ptr(sink),
+        c_int(1 if values_in_keys else 0), _stream()))
     return out
 
 

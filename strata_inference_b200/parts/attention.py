@@ -455,4 +455,175 @@ class Attention:
         return rt.linear(out, self.w_o)
 
 
+class LatentAttention:
+    """Attention whose keys and values of all heads are made from one low-rank row per
+    position (the latent c = rms_norm(down(x)[:rank]) * weight) and one rotated key part of
+    ``rot_dim`` columns that the heads share; only these are cached.
+
+    Parameters: ``num_heads``, ``head_dim`` (unrotated query/key columns of a head),
+    ``rot_dim`` (rotated ones, behind them), ``value_dim``, ``kv_rank``, ``score_scale``,
+    ``window`` (0: none), ``norm_eps``, ``position`` (a rotary part, applied to the rotated
+    columns of q and to the shared key part), ``sink`` (one stored number per head whose
+    exponential joins the softmax's denominator), ``head_gate`` (sigmoid(g_proj x) per head
+    on the head's output).
+
+        q_h = [a_h | r_h] = q_proj x (per head);  k_h = [U_h c | rot(k_r)],  v_h = V_h c
+        score_h(t, j) = (<a_h(t), U_h c(j)> + <rot(r_h(t)), rot(k_r(j))>) * score_scale
+
+    The scores are taken against the cached rows themselves: <a_h, U_h c> = <U_h^T a_h, c>, so
+    a query head becomes [U_h^T a_h | rot(r_h)], every head attends over the ONE row
+    [c | rot(k_r)] per position, the weighted sum of the c rows comes out of the attention
+    kernel, and V_h is applied to that sum (csrc/head_prepare.cu latent_prepare,
+    csrc/attention_rows.cu with ``values_in_keys``).  The two per-head products are batched
+    library products; softmax, sink and sums are 32-bit.
+    """
+
+    captures_prompts = True      # sequences, slots and counts are read on the device only
+
+    @staticmethod
+    def _sizes(params: Mapping):
+        nh, qd, rd = int(params["num_heads"]), int(params["head_dim"]), int(params.get("rot_dim") or 0)
+        vd, rank = int(params["value_dim"]), int(params["kv_rank"])
+        if min(nh, qd, vd, rank) <= 0 or rd < 0:
+            raise ConfigError(f"latent_attention: {nh} heads of {qd} + {rd}, values of {vd}, rank {rank}")
+        pad = -(-(rank + rd) // 16) * 16
+        if pad > 512:
+            raise ConfigError(f"latent_attention: kv_rank + rot_dim = {rank + rd} exceeds 512")
+        return nh, qd, rd, vd, rank, pad
+
+    @classmethod
+    def tensors(cls, params: Mapping, hidden: int) -> Dict[str, TensorDecl]:
+        nh, qd, rd, vd, rank, _ = cls._sizes(params)
+        out = {
+            "q_proj.weight": TensorDecl((nh * (qd + rd), hidden)),
+            "dkv_proj.weight": TensorDecl((rank + rd, hidden)),
+            "dkv_norm.weight": TensorDecl((rank,), init="norm"),
+            "uk_proj.weight": TensorDecl((nh * qd, rank)),
+            "uv_proj.weight": TensorDecl((nh * vd, rank)),
+            "o_proj.weight": TensorDecl((hidden, nh * vd)),
+        }
+        if params.get("sink"):
+            out["sink"] = TensorDecl((nh,), init="norm")
+        if params.get("head_gate"):
+            out["g_proj.weight"] = TensorDecl((nh, hidden))
+        return out
+
+    @classmethod
+    def resident(cls, params: Mapping, hidden: int) -> Dict[str, Resident]:
+        """The query heads, the down projection and the gates as ONE matrix."""
+        nh, qd, rd, vd, rank, _ = cls._sizes(params)
+        n_q = nh * (qd + rd)
+        pieces = (Piece("q_proj.weight", 0), Piece("dkv_proj.weight", n_q))
+        n_in = n_q + rank + rd
+        if params.get("head_gate"):
+            pieces += (Piece("g_proj.weight", n_in),)
+            n_in += nh
+        out = {
+            "in_proj.weight": Resident((n_in, hidden), pieces=pieces),
+            "dkv_norm.gain": Resident((rank,), torch.float32, (Piece("dkv_norm.weight"),)),
+            "uk_proj.weight": Resident((nh * qd, rank), pieces=(Piece("uk_proj.weight"),)),
+            "uv_proj.weight": Resident((nh * vd, rank), pieces=(Piece("uv_proj.weight"),)),
+            "o_proj.weight": Resident((hidden, nh * vd), pieces=(Piece("o_proj.weight"),)),
+        }
+        if params.get("sink"):
+            out["sink"] = Resident((nh,), torch.float32, (Piece("sink"),))
+        return out
+
+    def __init__(self, params: Mapping, hidden: int, weights: Mapping[str, torch.Tensor], rt):
+        self.rt = rt
+        self.nh, self.qd, self.rd, self.vd, self.rank, self.kw = self._sizes(params)
+        self.scale = float(params["score_scale"])
+        self.window = int(params.get("window") or 0)
+        self.eps = float(params["norm_eps"])
+        pos: PartSpec = params.get("position") or PartSpec("none", {})
+        position = part_class("position", pos.kind)(pos.params, max(self.rd, 2), {}, rt) \
+            if self.rd else None
+        self.inv_freq, self.rot = None, 0
+        if position is not None:
+            if not hasattr(position, "rotary"):
+                raise ConfigError("latent_attention: the position part must offer rotary()")
+            self.inv_freq, self.rot, style = position.rotary()
+            if self.rot and style != native.ROPE_INTERLEAVED:
+                raise ConfigError("latent_attention: the rotated columns are rotated in neighbouring pairs")
+        self.head_gate = bool(params.get("head_gate"))
+        self.n_q = self.nh * (self.qd + self.rd)
+        self.w_in = rt.cast_matrix(weights["in_proj.weight"])
+        self.c_gain = weights["dkv_norm.gain"]
+        # per head: U_h [qd, rank] (q times it) and V_h^T [rank, vd] (the summed latents times it)
+        self.w_uk = rt.cast_matrix(weights["uk_proj.weight"]).view(self.nh, self.qd, self.rank)
+        self.w_uv_t = rt.cast_matrix(weights["uv_proj.weight"]).view(self.nh, self.vd, self.rank).transpose(1, 2)
+        self.w_o = rt.cast_matrix(weights["o_proj.weight"])
+        self.sink = weights.get("sink")
+        self._target_warps = _WARPS_PER_SM * rt.sm_count
+
+    def cache_need(self) -> Optional[CacheNeed]:
+        return CacheNeed(kv=KVNeed(1, self.kw, self.window, values_in_keys=True))
+
+    def _splits(self, ctx, capacity: int) -> int:
+        """Runs of keys a (row, head) is cut into: as many as fill the device once, none
+        shorter than 32 keys."""
+        longest = (min(ctx.span or capacity, capacity)) if ctx.graph_capture else ctx.max_end
+        if self.window > 0:
+            longest = min(longest, self.window)
+        want = max(1, self._target_warps // max(1, ctx.n_rows * self.nh))
+        return max(1, min(want, -(-longest // 32), 128))
+
+    def forward(self, x: torch.Tensor, ctx, entry: int, cache_entry: int,
+                owns_cache: bool) -> torch.Tensor:
+        if not owns_cache:
+            raise ValueError("latent_attention: reading another run's cache is not built")
+        rt, nh, qd, rd, rank, kw = self.rt, self.nh, self.qd, self.rd, self.rank, self.kw
+        R = x.shape[0]
+        view = ctx.kv(cache_entry)
+        fresh = ctx.all_from_start
+        if not fresh and view.ring_tokens > 0 and not ctx.graph_capture:
+            room = view.ring_tokens - self.window + 1
+            for start, n in zip(ctx.starts, ctx.counts):
+                if n > room and start + n > view.ring_tokens:
+                    raise ValueError(
+                        f"a step may add at most {max(room, view.ring_tokens - start)} positions "
+                        f"to a sequence of {start} whose layers keep a window of {self.window} "
+                        f"in a ring of {view.ring_tokens}; got {n}")
+        proj = rt.linear(x, self.w_in)
+        rt.flush()
+        # the unrotated query columns of every head into the latent's space: [heads, rows, rank]
+        q_heads = proj[:, :self.n_q].view(R, nh, qd + rd)[:, :, :qd].transpose(0, 1)
+        with native.profile_region("library product (queries into the latent space)",
+                                   (nh * qd * rank + R * nh * (qd + rank)) * proj.element_size(),
+                                   2.0 * R * nh * qd * rank):
+            q_lat = torch.bmm(q_heads, self.w_uk)
+        q_rows = torch.empty((R, nh * kw), dtype=proj.dtype, device=proj.device)
+        k_rows = torch.empty((R, kw), dtype=proj.dtype, device=proj.device)
+        native.latent_prepare(proj, q_lat, q_rows, k_rows, self.c_gain, self.eps, self.inv_freq,
+                              self.rot, ctx, view.k, view.page_table, view.page_tokens,
+                              view.ring_tokens, nh, qd, rd, rank, kw)
+        out = torch.empty((R, nh * kw), dtype=proj.dtype, device=proj.device)
+        if fresh:
+            native.attention_rows(q_rows, nh * kw, k_rows, k_rows, kw, None, None, None,
+                                  view.page_tokens, view.ring_tokens, ctx.row_pos, ctx.row_seq,
+                                  ctx.seq_slot, ctx.seq_start, ctx.seq_row0, out, None, nh, 1, kw,
+                                  self.scale, 0.0, self.window, 1, sink=self.sink, values_in_keys=True)
+        else:
+            splits = self._splits(ctx, ctx.cache.max_seq_len)
+            scratch = None
+            if splits > 1:
+                scratch = rt.scratch(native.attention_rows_scratch_bytes(R, nh, kw, splits))
+            native.attention_rows(q_rows, nh * kw, None, None, kw, view.k, view.k, view.page_table,
+                                  view.page_tokens, view.ring_tokens, ctx.row_pos, ctx.row_seq,
+                                  ctx.seq_slot, ctx.seq_start, ctx.seq_row0, out, scratch, nh, 1, kw,
+                                  self.scale, 0.0, self.window, splits, sink=self.sink,
+                                  values_in_keys=True)
+        # the heads' summed latents (gated), then V_h per head
+        lat = torch.empty((R, nh * rank), dtype=out.dtype, device=out.device)
+        gate = proj[:, self.n_q + rank + rd:self.n_q + rank + rd + nh] if self.head_gate else None
+        native.head_gate(out, gate, lat, nh, rank, kw)
+        with native.profile_region("library product (summed latents to values)",
+                                   (nh * self.vd * rank + R * nh * (self.vd + rank)) * out.element_size(),
+                                   2.0 * R * nh * self.vd * rank):
+            vals = torch.bmm(lat.view(R, nh, rank).transpose(0, 1), self.w_uv_t)     # [heads, rows, vd]
+            vals = vals.transpose(0, 1).reshape(R, nh * self.vd)
+        return rt.linear(vals, self.w_o)
+
+
 register_mixer("attention", Attention)
+register_mixer("latent_attention", LatentAttention)

@@ -14,7 +14,8 @@ that norms a sub-layer's output only: h += post(sublayer(h)).  The
 residual stream h is kept and summed in 32-bit.  When the norms around an
 add are RMS norms the block runs "norm of the sub-layer's output, add, norm
 for the next sub-layer" as one kernel (csrc/norm.cu add_rms_norm), reaching
-over to the next block's first norm when the model passes it.
+over to the next block's first norm when the model passes it; Dynamic Tanh norms around an
+add are fused in the same way (add_dyt_norm).
 """
 
 from __future__ import annotations
@@ -24,11 +25,16 @@ from typing import Mapping, Optional
 import torch
 
 from ..config.spec import ConfigError
+from ..kernels import native
 from .registry import register_block
 
 
 def _fusable(norm) -> bool:
     return norm is None or getattr(norm, "fusable_rms", False)
+
+
+def _fusable_dyt(norm) -> bool:
+    return norm is None or getattr(norm, "fusable_dyt", False)
 
 
 class SandwichBlock:
@@ -79,6 +85,13 @@ class SandwichBlock:
                                  post.eps if post is not None else 0.0, h,
                                  nxt.gain if nxt is not None else None,
                                  nxt.eps if nxt is not None else 0.0, out)
+            return out
+        if _fusable_dyt(post) and _fusable_dyt(nxt):
+            # Dynamic Tanh on both sides of the add: the same step as one element-wise kernel
+            self.rt.flush()
+            out = torch.empty_like(y) if nxt is not None else None
+            native.add_dyt_norm(y, post.triple if post is not None else None, h,
+                                nxt.triple if nxt is not None else None, out)
             return out
         self.rt.flush()         # the steps below read y and h outside the chain
         if post is not None:

@@ -1,4 +1,4 @@
-"""The dense gated feed-forward: down(act(gate(x)) * up(x)), no biases; act is the
+"""``gated_mlp``: the dense gated feed-forward: down(act(gate(x)) * up(x)), no biases; act is the
 tanh-GELU or SiLU (``activation``: "gelu_pytorch_tanh", "silu").
 
 Reference: src/model/layer.rs:696-710 (two products, the gated activation,
@@ -8,6 +8,9 @@ the intermediate size allows it their rows are interleaved in groups of 8
 (8 gate rows, then the 8 matching up rows), which puts a gate value and its
 up value into the same thread of the weight-streaming kernel, whose epilogue
 then writes act(gate) * up directly.
+
+``mlp``: the feed-forward without a gate, down(act(up(x))), no biases; act is the square of
+relu (``activation``: "relu_squared"), the tanh-GELU or SiLU.
 """
 
 from __future__ import annotations
@@ -84,4 +87,41 @@ class GatedMLP:
         return rt.linear(t, self.w_down)
 
 
+_PLAIN_ACTIVATIONS = {"relu_squared": native.ACT_RELU_SQUARED, "gelu_pytorch_tanh": native.ACT_GELU_TANH,
+                      "silu": native.ACT_SILU}
+
+
+class PlainMLP:
+    captures_prompts = True   # row-wise: a recorded step of prompts may be replayed for others
+
+    @staticmethod
+    def tensors(params: Mapping, hidden: int) -> Dict[str, TensorDecl]:
+        inter = params["intermediate_size"]
+        return {"up_proj.weight": TensorDecl((inter, hidden)),
+                "down_proj.weight": TensorDecl((hidden, inter))}
+
+    @staticmethod
+    def resident(params: Mapping, hidden: int) -> Dict[str, Resident]:
+        inter = int(params["intermediate_size"])
+        return {"up_proj.weight": Resident((inter, hidden), pieces=(Piece("up_proj.weight"),)),
+                "down_proj.weight": Resident((hidden, inter), pieces=(Piece("down_proj.weight"),))}
+
+    def __init__(self, params: Mapping, hidden: int, weights: Mapping[str, torch.Tensor], rt):
+        self.rt = rt
+        self.inter = int(params["intermediate_size"])
+        act = params.get("activation", "relu_squared")
+        if act not in _PLAIN_ACTIVATIONS:
+            raise ConfigError(f"mlp: activation {act!r} is not supported; "
+                              f"known: {', '.join(_PLAIN_ACTIVATIONS)}")
+        self.act = _PLAIN_ACTIVATIONS[act]
+        self.w_up = rt.cast_matrix(weights["up_proj.weight"])
+        self.w_down = rt.cast_matrix(weights["down_proj.weight"])
+
+    def forward(self, x: torch.Tensor, ctx) -> torch.Tensor:
+        up = self.rt.linear(x, self.w_up)
+        native.activate(up, up, self.act)
+        return self.rt.linear(up, self.w_down)
+
+
 register_feed_forward("gated_mlp", GatedMLP)
+register_feed_forward("mlp", PlainMLP)

@@ -10,6 +10,11 @@ the weights are placed on the device.
 activations, unchanged.  A layer whose sub-layers read the stream itself and are normed
 on the way out only (x <- x + norm(sublayer(x))) names it at its two "pre" sites, so
 that the block arrangements and their fused "norm, add, norm" step serve it as they are.
+
+``dynamic_tanh`` is a norm without statistics: tanh(alpha x) * weight + b, element by
+element in 32-bit, with one stored number ``alpha`` and one ``weight`` and ``b`` per
+column.  Blocks fuse it into the residual add as they fuse the RMS norm (``fusable_dyt``,
+csrc/norm.cu add_dyt_norm).
 """
 
 from __future__ import annotations
@@ -77,5 +82,38 @@ class IdentityNorm:
         return native.cast_rows(x, out)
 
 
+class DynamicTanh:
+    fusable_rms = False
+    fusable_dyt = True
+
+    @staticmethod
+    def tensors(params: Mapping, hidden: int) -> Dict[str, TensorDecl]:
+        return {"weight": TensorDecl((hidden,), init="norm"), "b": TensorDecl((hidden,), init="norm"),
+                "alpha": TensorDecl((), init="norm")}
+
+    @staticmethod
+    def resident(params: Mapping, hidden: int) -> Dict[str, Resident]:
+        return {"weight": Resident((hidden,), torch.float32, (Piece("weight"),)),
+                "b": Resident((hidden,), torch.float32, (Piece("b"),)),
+                "alpha": Resident((1,), torch.float32, (Piece("alpha"),))}
+
+    def __init__(self, params: Mapping, hidden: int, weights: Mapping[str, torch.Tensor], rt):
+        self.hidden = hidden
+        self.rt = rt
+        self.weight, self.b, self.alpha = weights["weight"], weights["b"], weights["alpha"]
+
+    @property
+    def triple(self):
+        """(weight, b, alpha) as the fused residual kernel takes them."""
+        return self.weight, self.b, self.alpha
+
+    def forward(self, x: torch.Tensor, out_dtype: Optional[torch.dtype] = None,
+                rows: Optional[torch.Tensor] = None) -> torch.Tensor:
+        n = x.shape[0] if rows is None else rows.numel()
+        out = torch.empty((n, self.hidden), dtype=out_dtype or self.rt.dtype, device=x.device)
+        return native.dyt_norm(x, self.weight, self.b, self.alpha, out, rows)
+
+
 register_norm("rms_norm", RMSNorm)
+register_norm("dynamic_tanh", DynamicTanh)
 register_norm("identity", IdentityNorm)

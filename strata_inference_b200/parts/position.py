@@ -6,6 +6,7 @@ reference: freq_i = theta^((-1/rot) * 2i) evaluated in 32-bit
 (src/backend/cpu.rs:1276-1282); the angle pos * freq_i and its sine and
 cosine are taken in 32-bit inside the kernel (csrc/rope_cache.cu).
 ``scaling_factor`` (default 1) divides every frequency: positions stretched linearly.
+``frequencies: "float64"`` evaluates theta^(-2i/rot) in 64-bit and rounds once to 32-bit.
 ``none``: no encoding.
 
 A position part offers ``rotary()`` -> (inv_freq, rotary_dim, style) for the
@@ -39,9 +40,14 @@ class Rope:
         if self.rotary_dim % 2 or not 0 < self.rotary_dim <= head_dim:
             raise ConfigError(f"rotary_dim {self.rotary_dim} must be even and at most "
                               f"head_dim {head_dim}")
-        inv_ndims = torch.tensor(-1.0 / self.rotary_dim, dtype=torch.float32)
-        two_i = torch.arange(self.rotary_dim // 2, dtype=torch.float32) * 2.0
-        freqs = torch.pow(torch.tensor(self.theta, dtype=torch.float32), inv_ndims * two_i)
+        if params.get("frequencies") == "float64":
+            two_i = torch.arange(self.rotary_dim // 2, dtype=torch.float64) * 2.0
+            freqs = torch.pow(torch.tensor(self.theta, dtype=torch.float64),
+                              -two_i / self.rotary_dim).to(torch.float32)
+        else:
+            inv_ndims = torch.tensor(-1.0 / self.rotary_dim, dtype=torch.float32)
+            two_i = torch.arange(self.rotary_dim // 2, dtype=torch.float32) * 2.0
+            freqs = torch.pow(torch.tensor(self.theta, dtype=torch.float32), inv_ndims * two_i)
         self.scaling_factor = float(params.get("scaling_factor") or 1.0)
         if self.scaling_factor <= 0:
             raise ConfigError(f"scaling_factor {self.scaling_factor} must be positive")

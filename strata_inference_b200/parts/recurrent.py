@@ -25,6 +25,14 @@ the recurrence besides the projections (unit norms, decays, gates, the state) is
         o = S^T q / (max(|n . q|, e^-m') + 1e-6),      q = q_proj x * head_dim^-1/2
     then per head o / rms(o), times norm.weight (one per head and dimension) and
     sigmoid(g_proj x), and o_proj.  State: S, n and m (m starts at 0).
+
+``retention``  linear attention with one fixed decay per head and no softmax or denominator.
+    Parameters: ``num_heads``, ``head_dim``, ``value_dim``, ``decay`` (one number per head),
+    ``key_scale`` (on k, after the rotation), ``norm_eps``, ``position`` (a PartSpec of a
+    rotary position part with half-split pairs, or "none").
+        q, k rotated by the token's position;  k <- key_scale k
+        S <- decay_h S + k v^T;  o = S^T q
+    then per head o / rms(o) (no weight), times silu(g_proj x), and o_proj.  State: S.
 """
 
 from __future__ import annotations
@@ -34,11 +42,11 @@ from typing import Dict, Mapping, Optional
 import torch
 
 from ..cache.paged import CacheNeed, StateNeed
-from ..config.spec import ConfigError
+from ..config.spec import ConfigError, PartSpec
 from ..kernels import native
 from ..weights.arena import Piece, Resident
 from ..weights.loader import TensorDecl
-from .registry import register_mixer
+from .registry import part_class, register_mixer
 
 
 def _pieces(rows):
@@ -215,5 +223,80 @@ class MatrixMemory:
         return rt.linear(y, self.w_o)
 
 
+class Retention:
+    captures_prompts = True      # sequences, slots and counts are read on the device only
+
+    @staticmethod
+    def _sizes(params: Mapping):
+        H, kd, vd = int(params["num_heads"]), int(params["head_dim"]), int(params["value_dim"])
+        if H <= 0 or not 0 < kd <= 512 or vd <= 0:
+            raise ConfigError(f"retention: {H} heads, head_dim {kd} (at most 512), value_dim {vd}")
+        if len(params["decay"]) != H:
+            raise ConfigError(f"retention: {len(params['decay'])} decays for {H} heads")
+        return H, kd, vd
+
+    @classmethod
+    def _in_rows(cls, params: Mapping):
+        H, kd, vd = cls._sizes(params)
+        return [("q_proj.weight", H * kd), ("k_proj.weight", H * kd), ("v_proj.weight", H * vd),
+                ("g_proj.weight", H * vd)]
+
+    @classmethod
+    def tensors(cls, params: Mapping, hidden: int) -> Dict[str, TensorDecl]:
+        H, kd, vd = cls._sizes(params)
+        out = {name: TensorDecl((n, hidden)) for name, n in cls._in_rows(params)}
+        out["o_proj.weight"] = TensorDecl((hidden, H * vd))
+        return out
+
+    @classmethod
+    def resident(cls, params: Mapping, hidden: int) -> Dict[str, Resident]:
+        H, kd, vd = cls._sizes(params)
+        pieces, n_in = _pieces(cls._in_rows(params))
+        return {"in_proj.weight": Resident((n_in, hidden), pieces=pieces),
+                "o_proj.weight": Resident((hidden, H * vd), pieces=(Piece("o_proj.weight"),))}
+
+    def __init__(self, params: Mapping, hidden: int, weights: Mapping[str, torch.Tensor], rt):
+        self.rt = rt
+        self.H, self.kd, self.vd = self._sizes(params)
+        self.eps = float(params["norm_eps"])
+        self.key_scale = float(params.get("key_scale", 1.0))
+        # (64-bit numbers of the configuration, rounded once)
+        self.decay = torch.tensor([float(d) for d in params["decay"]], dtype=torch.float64).to(
+            torch.float32).to(rt.device)
+        pos: PartSpec = params.get("position") or PartSpec("none", {})
+        position = part_class("position", pos.kind)(pos.params, self.kd, {}, rt)
+        if not hasattr(position, "rotary"):
+            raise ConfigError("retention: the position part must offer rotary()")
+        self.inv_freq, self.rot, style = position.rotary()
+        if self.rot and style != native.ROPE_HALF_SPLIT:
+            raise ConfigError("retention: q and k are rotated in half-split pairs")
+        self.w_in = rt.cast_matrix(weights["in_proj.weight"])
+        self.w_o = rt.cast_matrix(weights["o_proj.weight"])
+
+    def cache_need(self) -> Optional[CacheNeed]:
+        return CacheNeed(state=StateNeed((_round4(self.H * self.vd * self.kd),)))
+
+    def forward(self, x: torch.Tensor, ctx, entry: int, cache_entry: int,
+                owns_cache: bool) -> torch.Tensor:
+        if not owns_cache:
+            raise ValueError("retention: a recurrent state cannot be lent to another run")
+        rt, H, kd, vd = self.rt, self.H, self.kd, self.vd
+        R = x.shape[0]
+        state = ctx.state(cache_entry)
+        proj = rt.linear(x, self.w_in)
+        f32 = dict(dtype=torch.float32, device=x.device)
+        qn, kn = torch.empty((R, H * kd), **f32), torch.empty((R, H * kd), **f32)
+        vc = torch.empty((R, H * vd), **f32)
+        native.retention_prepare(proj, self.inv_freq, self.rot, ctx.row_pos, qn, kn, vc, H, kd, vd,
+                                 self.key_scale)
+        o = torch.empty((R, H * vd), **f32)
+        native.retention_scan(qn, kn, vc, self.decay, state, o, ctx, H, kd, vd)
+        y = torch.empty((R, H * vd), dtype=proj.dtype, device=x.device)
+        gate = proj[:, 2 * H * kd + H * vd:2 * H * kd + 2 * H * vd]
+        native.head_norm_gate(o, None, None, gate, y, H, vd, self.eps, native.GATE_SILU)
+        return rt.linear(y, self.w_o)
+
+
 register_mixer("gated_delta", GatedDeltaRule)
+register_mixer("retention", Retention)
 register_mixer("matrix_memory", MatrixMemory)

@@ -14,7 +14,7 @@ from ..config.spec import ConfigError, PartSpec
 
 _REGISTRIES: Dict[str, Dict[str, type]] = {
     "mixer": {}, "feed_forward": {}, "norm": {}, "position": {},
-    "block": {}, "embedding": {}, "head": {},
+    "block": {}, "embedding": {}, "head": {}, "joint": {},
 }
 
 
@@ -49,6 +49,11 @@ def register_embedding(kind: str, cls: type) -> type:
 
 def register_head(kind: str, cls: type) -> type:
     return _register("head", kind, cls)
+
+
+def register_joint(kind: str, cls: type) -> type:
+    """A part that joins two streams into one: ``forward(h, x0) -> h``."""
+    return _register("joint", kind, cls)
 
 
 def part_class(role: str, kind: str) -> type:

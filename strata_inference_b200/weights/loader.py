@@ -26,9 +26,10 @@ from .safetensors_io import ModelFiles
 class TensorDecl:
     """A tensor a part needs.  ``init`` tells the random-weights mode how to
     fill it: "matrix" (projection and embedding matrices) or "norm" (norm
-    weights); ``integer`` marks index tables."""
+    weights); ``integer`` marks index tables.  ``shape`` None (with ``optional``): a tensor
+    that a folder may hold and nothing reads; neither its shape nor its kind is checked."""
 
-    shape: Tuple[int, ...]
+    shape: Optional[Tuple[int, ...]]
     init: str = "matrix"
     optional: bool = False
     integer: bool = False
@@ -68,6 +69,8 @@ def check_table(where: str, have: Mapping[str, Tuple[Tuple[int, ...], torch.dtyp
         if n not in have:
             continue
         shape, dtype = have[n]
+        if d.shape is None:
+            continue
         if tuple(shape) != tuple(d.shape):
             wrong_shape.append((n, tuple(shape), tuple(d.shape)))
         if d.integer and dtype.is_floating_point:
