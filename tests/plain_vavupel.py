@@ -63,7 +63,7 @@ def latent_attention(h, w, m, eps):
     every head; the window and the sink enter a plain softmax over the visible keys."""
     n = h.shape[0]
     H, d, r, vd, rank = m["heads"], m["dim"], m["rot_dim"], m["vdim"], m["kv_rank"]
-    window = m["mask"]["size"]
+    window = m["mask"]["size"] if m.get("mask") else n      # (no mask: every earlier position)
     pos = np.arange(n)
     q = (h @ w["q"].T).reshape(n, H, d + r)
     down = h @ w["dkv"].T
@@ -90,8 +90,10 @@ def retention(h, w, m, eps):
     n = h.shape[0]
     H, d, vd = m["heads"], m["dim"], m["vdim"]
     pos = np.arange(n)
-    q = rotate((h @ w["q"].T).reshape(n, H, d), pos, m["rot"]["dims"], m["rot"]["base"], False)
-    k = rotate((h @ w["k"].T).reshape(n, H, d), pos, m["rot"]["dims"], m["rot"]["base"], False)
+    q, k = (h @ w["q"].T).reshape(n, H, d), (h @ w["k"].T).reshape(n, H, d)
+    if m.get("rot"):
+        q = rotate(q, pos, m["rot"]["dims"], m["rot"]["base"], False)
+        k = rotate(k, pos, m["rot"]["dims"], m["rot"]["base"], False)
     k = k * d ** -0.5
     v = (h @ w["v"].T).reshape(n, H, vd)
     o = np.zeros((n, H, vd))
