@@ -465,6 +465,26 @@ def karupel_config(size):
             "layers": [pattern[i % 4] for i in range(n_layers)]}
 
 
+def vavupel_config(size):
+    """Vavupel at these sizes: retention, latent attention, retention, ..., every layer with a
+    feed-forward of the same width as the other models' (two matrices instead of three), the
+    middle layers inside a loop that is walked once (one stream-mix product); retention keeps
+    matrices of 128 x head width, the latent is 448 wide with 64 rotated columns beside it."""
+    width, ff, heads, kv, hd, vocab, n_layers = KARUPEL_SIZES[size]
+    mlp = {"kind": "dense", "ff": ff}
+    ret = {"type": "retention", "mlp": mlp, "mixer": {
+        "heads": heads, "dim": 128, "vdim": hd, "decay": [1.0 - 2.0 ** -(5 + i % 4) for i in range(heads)],
+        "rot": {"base": 10000.0, "dims": 128}}}
+    lat = {"type": "latent_attention", "mlp": mlp, "mixer": {
+        "heads": heads, "dim": 128, "rot_dim": 64, "vdim": 128, "kv_rank": 448, "scale": 192 ** -0.5,
+        "mask": {"size": 4096}, "rot": {"base": 10000.0, "dims": 64}}}
+    pattern = [ret, lat]
+    return {"architecture": "Vavupel", "vocab": vocab, "width": width, "norm": {"eps": 1e-6},
+            "embedding": {"scale": 1.0, "bigram": {"buckets": 65521, "mul_prev": 31, "mul_cur": 7}},
+            "layers": [pattern[i % 2] for i in range(n_layers)],
+            "loop": {"start": 2, "stop": n_layers - 2, "times": 1}, "logit_softcap": 30.0}
+
+
 def gemma2_config_like(size):
     width, ff, heads, kv, hd, vocab, n_layers = KARUPEL_SIZES[size]
     cfg = baseline_config()
@@ -479,9 +499,10 @@ def state_bytes_per_step(engine, batch):
     return sum(2 * batch * t[0].numel() * t.element_size() for t in engine.cache.state.values())
 
 
-def run_karupel(args):
-    """Karupel beside Gemma2 at equal layer sizes: a prompt step and single-token steps, and
-    (``--kernels``) the per-kernel tables of both, on standard output; one JSON line at the end."""
+def run_karupel(args, pair=None, title="Karupel beside Gemma2"):
+    """Two architectures at equal layer sizes (Karupel beside Gemma2; with ``--vavupel`` Vavupel
+    beside Karupel): a prompt step and single-token steps, and (``--kernels``) the per-kernel
+    tables of both, on standard output; one JSON line at the end."""
     import gc
     import torch
     from strata_inference_b200 import GenerationEngine
@@ -492,7 +513,8 @@ def run_karupel(args):
     sizes = [args.size] if args.size else sorted(KARUPEL_SIZES)
     out = {}
     for size in sizes:
-        for name, cfg in (("karupel", karupel_config(size)), ("gemma2", gemma2_config_like(size))):
+        for name, make in pair or (("karupel", karupel_config), ("gemma2", gemma2_config_like)):
+            cfg = make(size)
             batches = [1, 8, 64]
             gen = GenerationEngine.from_random(cfg, seed=5, dtype="bfloat16", ctx=context,
                                                max_tokens=max(batches) * context,
@@ -531,8 +553,7 @@ def run_karupel(args):
             del gen, engine
             gc.collect()
             torch.cuda.empty_cache()
-    print(json.dumps({"comparison": "Karupel beside Gemma2 at equal layer sizes (8 layers, bf16, "
-                      "random weights)", "context": context, "prompt_tokens": T,
+    print(json.dumps({"comparison": title + " at equal layer sizes (8 layers, bf16, random weights)", "context": context, "prompt_tokens": T,
                       "peaks": peaks, "results": out}))
     return 0
 
@@ -558,8 +579,11 @@ def main():
     ap.add_argument("--karupel", action="store_true",
                     help="instead of the timed run: Karupel beside Gemma2 at equal layer sizes "
                          "(--size; with --kernels also the per-kernel tables of both)")
+    ap.add_argument("--vavupel", action="store_true",
+                    help="instead of the timed run: Vavupel beside Karupel at equal layer sizes "
+                         "(--size; with --kernels also the per-kernel tables of both)")
     ap.add_argument("--size", default="", choices=[""] + sorted(KARUPEL_SIZES),
-                    help="with --karupel: one of the sizes (default: all)")
+                    help="with --karupel or --vavupel: one of the sizes (default: all)")
     ap.add_argument("--shape", default="2b", choices=sorted(SHAPES),
                     help="layer sizes: the 2B shape (the recorded line) or the 9B / 27B shapes")
     args = ap.parse_args()
@@ -574,6 +598,9 @@ def main():
         return 2
     if args.warmup < 3:
         args.warmup = 3
+    if args.vavupel:
+        return run_karupel(args, (("vavupel", vavupel_config), ("karupel", karupel_config)),
+                           "Vavupel beside Karupel")
     if args.karupel:
         return run_karupel(args)
     if args.kernels:

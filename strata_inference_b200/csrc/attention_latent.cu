@@ -1,0 +1,355 @@
+// Attention over ONE shared row per position (a latent that is key and value of every head
+// at once) on the tensor cores, bfloat16 storage, 32-bit scores, softmax and sums: the prompt
+// and the single-token kernel of the latent attention mixer.
+//
+// A query head h of row r is a vector q[r, h, :kw]; position j of the row's sequence holds one
+// row c_j[:kw] (in the step's packed rows, or in the paged cache with one "kv head").  With
+//     s_j = scale <q[r, h], c_j>,   visible j: max(0, p - window + 1) <= j <= p  (window 0: all)
+//     out[r, h, :] = (sum_j e^{s_j - M} c_j) / (sum_j e^{s_j - M} + e^{sink_h - M})
+// every head reads the same rows, so a block takes a tile of up to 16 (row, head) pairs as the
+// M side of mma.sync.m16n8k16 and walks the keys 16 at a time: a key tile is fetched ONCE
+// (cp.async, two buffers in turn) and serves all heads as the B operand of the scores
+// (S = Q C^T, the block's 4 warps split kw and add their parts through shared memory) and,
+// transposed by ldmatrix, of the weighted sum (O += P C, the warps split the columns).  A tile
+// holds 16 heads of one row, or with fewer than 16 heads the heads of several consecutive
+// rows; rows of a tile that belong to different sequences are worked on one sequence after
+// the other, the others masked.  With splits > 1 a tile's run of keys is cut and the parts
+// (max, sum, accumulator) go to scratch memory in the layout of attention_rows.cu, whose
+// combine kernel merges them and adds the sink.
+//
+// The caller keeps the leading columns of `out` that are values (the latent's rank).
+// Plain counterpart: tests/plain_vavupel.py latent_attention().
+#include "common.cuh"
+
+int sib_launch_attention_combine_sink_bf16(const float* partial, void* out, int units, int splits,
+                                           int head_dim, const float* sink, int n_heads,
+                                           cudaStream_t s);
+
+namespace {
+
+struct LatentArgs {
+    const __nv_bfloat16* q;        // [rows, n_heads * kw]
+    const __nv_bfloat16* k_new;    // [rows, kw] of this step (null: keys come from the cache)
+    const __nv_bfloat16* k_pool;   // [pages, 1, page_tokens, kw]
+    __nv_bfloat16* out;            // [rows, n_heads * kw]
+    float* partial;                // [rows, n_heads, splits, kw + 2] when splits > 1
+    const float* sink;             // [n_heads] or null
+    const int* row_pos;
+    const int* row_seq;
+    const int* seq_slot;
+    const int* seq_start;
+    const int* seq_row0;
+    const int* page_table;
+    int rows, n_heads, kw;
+    int rpt;                       // rows of a tile (1 with 16 heads or more)
+    int head_chunks;               // tiles a row's heads are cut into
+    int max_pages, page_tokens, ring_tokens;
+    int window, splits;
+    float scale;
+};
+
+constexpr int KT = 16;             // keys of a tile
+constexpr int PADW = 8;            // bfloat16 elements between the rows of a staged tile
+
+__device__ __forceinline__ void cp16(void* smem, const void* gmem, bool valid) {
+    const uint32_t s = (uint32_t)__cvta_generic_to_shared(smem);
+    const int bytes = valid ? 16 : 0;   // 0: the chunk is filled with zeros
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(s), "l"(gmem), "r"(bytes));
+}
+__device__ __forceinline__ void cp_commit() { asm volatile("cp.async.commit_group;\n" ::); }
+template <int N> __device__ __forceinline__ void cp_wait() {
+    asm volatile("cp.async.wait_group %0;\n" ::"n"(N));
+}
+__device__ __forceinline__ void ldsm_x2_trans(uint32_t& r0, uint32_t& r1, const void* smem) {
+    const uint32_t s = (uint32_t)__cvta_generic_to_shared(smem);
+    asm volatile("ldmatrix.sync.aligned.m8n8.x2.trans.shared.b16 {%0,%1}, [%2];\n"
+                 : "=r"(r0), "=r"(r1) : "r"(s));
+}
+__device__ __forceinline__ void mma16816(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 "
+        "{%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+        : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+        : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ uint32_t pack2(float lo, float hi) {
+    const __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<const uint32_t*>(&v);
+}
+
+// KSW: 16-column steps of kw that one warp multiplies (kw <= 64 KSW); NT: 8-column tiles of
+// the output that one warp sums (kw <= 32 NT).
+template <int KSW, int NT>
+__global__ void __launch_bounds__(128) latent_attention_kernel(LatentArgs p) {
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    pdl_trigger();
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int kw = p.kw, ldk = kw + PADW;
+    __nv_bfloat16* tiles = reinterpret_cast<__nv_bfloat16*>(smem_raw);           // [2][KT][ldk]
+    float* red = reinterpret_cast<float*>(smem_raw + (size_t)2 * KT * ldk * sizeof(__nv_bfloat16));  // [4][32][8]
+    const int n_ksteps = kw / 16, n_ntiles = kw / 8;
+    const int chunk = blockIdx.x % p.head_chunks;
+    const int r0 = (blockIdx.x / p.head_chunks) * p.rpt;
+    const int split = blockIdx.y;
+    const int rows_here = min(p.rpt, p.rows - r0);
+    const int heads_here = min(16, p.n_heads - chunk * 16);
+    // the two rows of the M side that this thread holds in accumulators: i0 and i0 + 8
+    const int g4 = lane >> 2, q4 = lane & 3;
+    int my_row[2], my_head[2];
+    bool my_valid[2];
+#pragma unroll
+    for (int e = 0; e < 2; ++e) {
+        const int i = g4 + 8 * e;
+        int rr, hh;
+        if (p.rpt == 1) { rr = 0; hh = i; }
+        else { rr = i / p.n_heads; hh = i % p.n_heads; }
+        my_valid[e] = rr < rows_here && hh < heads_here;
+        my_row[e] = r0 + rr;
+        my_head[e] = chunk * 16 + hh;
+    }
+    pdl_wait();
+    // this warp's steps of the queries, as A fragments (steps warp, warp + 4, ...)
+    uint32_t qa[KSW][4];
+#pragma unroll
+    for (int s = 0; s < KSW; ++s) {
+        const int ks = warp + 4 * s;
+#pragma unroll
+        for (int e = 0; e < 4; ++e) qa[s][e] = 0u;
+        if (ks < n_ksteps) {
+#pragma unroll
+            for (int e = 0; e < 2; ++e)
+                if (my_valid[e]) {
+                    const __nv_bfloat16* src = p.q + ((size_t)my_row[e] * p.n_heads + my_head[e]) * kw + ks * 16 + 2 * q4;
+                    qa[s][e] = *reinterpret_cast<const uint32_t*>(src);
+                    qa[s][e + 2] = *reinterpret_cast<const uint32_t*>(src + 8);
+                }
+        }
+    }
+    float o[NT][4];
+#pragma unroll
+    for (int t = 0; t < NT; ++t)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) o[t][e] = 0.f;
+    float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};
+
+    // one sequence's rows of the tile after the other
+    int done = 0;
+    while (done < rows_here) {
+        const int b = p.row_seq[r0 + done];
+        int cnt = 1;
+        while (done + cnt < rows_here && p.row_seq[r0 + done + cnt] == b) ++cnt;
+        const int slot = p.seq_slot[b], start = p.seq_start[b], row0 = p.seq_row0[b];
+        // (rows of one sequence follow one another in position)
+        const int pos_first = p.row_pos[r0 + done], pos_last = p.row_pos[r0 + done + cnt - 1];
+        const int lo_all = p.window > 0 ? max(0, pos_first - p.window + 1) : 0;
+        const int span = pos_last - lo_all + 1;
+        int per = (span + p.splits - 1) / p.splits;
+        per = (per + KT - 1) / KT * KT;
+        const int j0 = lo_all + split * per;
+        const int j1 = min(j0 + per, pos_last + 1);
+        bool act[2];
+        int pos[2], lo[2];
+#pragma unroll
+        for (int e = 0; e < 2; ++e) {
+            const int rr = my_row[e] - r0;
+            act[e] = my_valid[e] && rr >= done && rr < done + cnt;
+            pos[e] = act[e] ? p.row_pos[my_row[e]] : -1;
+            lo[e] = p.window > 0 ? max(0, pos[e] - p.window + 1) : 0;
+        }
+        const int n_tiles = j1 > j0 ? (j1 - j0 + KT - 1) / KT : 0;
+        const int chunks_per_key = kw / 8;
+        auto fetch = [&](int t) {
+            __nv_bfloat16* dst = tiles + (size_t)(t & 1) * KT * ldk;
+            for (int c = tid; c < KT * chunks_per_key; c += 128) {
+                const int key = c / chunks_per_key, part = c - key * chunks_per_key;
+                const int j = j0 + t * KT + key;
+                const bool valid = j < j1;
+                const __nv_bfloat16* src = p.q;      // (any valid address: nothing is read when !valid)
+                if (valid) {
+                    if (p.k_new && j >= start) {
+                        src = p.k_new + (size_t)(row0 + (j - start)) * kw;
+                    } else {
+                        const int cell = p.ring_tokens > 0 ? j % p.ring_tokens : j;
+                        const int page = p.page_table[(size_t)slot * p.max_pages + cell / p.page_tokens];
+                        src = p.k_pool + ((size_t)page * p.page_tokens + cell % p.page_tokens) * kw;
+                    }
+                    src += part * 8;
+                }
+                cp16(dst + (size_t)key * ldk + part * 8, src, valid);
+            }
+            cp_commit();
+        };
+        if (n_tiles > 0) fetch(0);
+        for (int t = 0; t < n_tiles; ++t) {
+            if (t + 1 < n_tiles) { fetch(t + 1); cp_wait<1>(); } else { cp_wait<0>(); }
+            __syncthreads();
+            const __nv_bfloat16* kt = tiles + (size_t)(t & 1) * KT * ldk;
+            // this warp's part of the scores: 16 units x 16 keys
+            float s[2][4];
+#pragma unroll
+            for (int n = 0; n < 2; ++n)
+#pragma unroll
+                for (int e = 0; e < 4; ++e) s[n][e] = 0.f;
+#pragma unroll
+            for (int sidx = 0; sidx < KSW; ++sidx) {
+                const int ks = warp + 4 * sidx;
+                if (ks < n_ksteps) {
+#pragma unroll
+                    for (int n = 0; n < 2; ++n) {
+                        const __nv_bfloat16* bp = kt + (size_t)(n * 8 + g4) * ldk + ks * 16 + 2 * q4;
+                        mma16816(s[n], qa[sidx], *reinterpret_cast<const uint32_t*>(bp),
+                                 *reinterpret_cast<const uint32_t*>(bp + 8));
+                    }
+                }
+            }
+            float* mine = red + ((size_t)warp * 32 + lane) * 8;
+#pragma unroll
+            for (int n = 0; n < 2; ++n)
+#pragma unroll
+                for (int e = 0; e < 4; ++e) mine[n * 4 + e] = s[n][e];
+            __syncthreads();
+#pragma unroll
+            for (int n = 0; n < 2; ++n)
+#pragma unroll
+                for (int e = 0; e < 4; ++e)
+                    s[n][e] = (red[(0 * 32 + lane) * 8 + n * 4 + e] + red[(1 * 32 + lane) * 8 + n * 4 + e]) +
+                              (red[(2 * 32 + lane) * 8 + n * 4 + e] + red[(3 * 32 + lane) * 8 + n * 4 + e]);
+            // scale, mask, running maximum (per row of the M side: e = 0 holds s[n][0..1], e = 1 s[n][2..3])
+            const int jt = j0 + t * KT;
+            float mx[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+            for (int n = 0; n < 2; ++n)
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    const int r = e >> 1;
+                    const int j = jt + n * 8 + 2 * q4 + (e & 1);
+                    const bool see = act[r] && j >= lo[r] && j <= pos[r] && j < j1;
+                    s[n][e] = see ? s[n][e] * p.scale : -INFINITY;
+                    mx[r] = fmaxf(mx[r], s[n][e]);
+                }
+            float corr[2];
+#pragma unroll
+            for (int r = 0; r < 2; ++r) {
+                mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 1));
+                mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 2));
+                const float m_new = fmaxf(m_run[r], mx[r]);
+                corr[r] = m_new == -INFINITY ? 1.f : expf(m_run[r] - m_new);    // (-inf - finite: 0)
+                m_run[r] = m_new;
+                l_run[r] *= corr[r];
+            }
+            float pr[2][4];
+#pragma unroll
+            for (int n = 0; n < 2; ++n)
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    const int r = e >> 1;
+                    pr[n][e] = s[n][e] == -INFINITY ? 0.f : expf(s[n][e] - m_run[r]);
+                    l_run[r] += pr[n][e];
+                }
+            uint32_t pa[4] = {pack2(pr[0][0], pr[0][1]), pack2(pr[0][2], pr[0][3]),
+                              pack2(pr[1][0], pr[1][1]), pack2(pr[1][2], pr[1][3])};
+            // the weighted sum of this warp's columns (tiles warp, warp + 4, ... of 8 columns)
+#pragma unroll
+            for (int ti = 0; ti < NT; ++ti) {
+                const int nt = warp + 4 * ti;
+                if (nt < n_ntiles) {
+                    o[ti][0] *= corr[0]; o[ti][1] *= corr[0];
+                    o[ti][2] *= corr[1]; o[ti][3] *= corr[1];
+                    uint32_t b0, b1;
+                    ldsm_x2_trans(b0, b1, kt + (size_t)(lane & 15) * ldk + nt * 8);
+                    mma16816(o[ti], pa, b0, b1);
+                }
+            }
+            __syncthreads();       // (the tile's buffer is fetched into again two tiles on)
+        }
+        done += cnt;
+    }
+    // the sums of a row over the four threads that hold its columns
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+        l_run[r] += __shfl_xor_sync(0xffffffffu, l_run[r], 1);
+        l_run[r] += __shfl_xor_sync(0xffffffffu, l_run[r], 2);
+    }
+    if (p.splits == 1) {
+        float inv[2];
+#pragma unroll
+        for (int r = 0; r < 2; ++r) {
+            float scale_o = 1.f, l = l_run[r];
+            if (p.sink && my_valid[r]) {
+                const float sk = p.sink[my_head[r]];
+                const float top = fmaxf(m_run[r], sk);
+                scale_o = m_run[r] == -INFINITY ? 0.f : expf(m_run[r] - top);
+                l = l * scale_o + expf(sk - top);
+            }
+            inv[r] = l > 0.f ? scale_o / l : 0.f;
+        }
+#pragma unroll
+        for (int ti = 0; ti < NT; ++ti) {
+            const int nt = warp + 4 * ti;
+            if (nt >= n_ntiles) continue;
+#pragma unroll
+            for (int r = 0; r < 2; ++r)
+                if (my_valid[r]) {
+                    __nv_bfloat16* dst = p.out + ((size_t)my_row[r] * p.n_heads + my_head[r]) * kw + nt * 8 + 2 * q4;
+                    *reinterpret_cast<uint32_t*>(dst) = pack2(o[ti][2 * r] * inv[r], o[ti][2 * r + 1] * inv[r]);
+                }
+        }
+    } else {
+#pragma unroll
+        for (int r = 0; r < 2; ++r) {
+            if (!my_valid[r]) continue;
+            float* pp = p.partial + (((size_t)my_row[r] * p.n_heads + my_head[r]) * p.splits + split) * (kw + 2);
+            if (warp == 0 && q4 == 0) { pp[0] = m_run[r]; pp[1] = l_run[r]; }
+#pragma unroll
+            for (int ti = 0; ti < NT; ++ti) {
+                const int nt = warp + 4 * ti;
+                if (nt < n_ntiles)
+                    *reinterpret_cast<float2*>(pp + 2 + nt * 8 + 2 * q4) = make_float2(o[ti][2 * r], o[ti][2 * r + 1]);
+            }
+        }
+    }
+}
+
+}  // namespace
+
+SIB_EXPORT int sib_attention_latent_supports(int n_heads, int kw) {
+    return n_heads > 0 && kw >= 16 && kw % 16 == 0 && kw <= 512;
+}
+
+SIB_EXPORT int sib_attention_latent(
+    const void* q, const void* k_new, const void* k_pool, const int* page_table, int max_pages,
+    int page_tokens, int ring_tokens, const int* row_pos, const int* row_seq, const int* seq_slot,
+    const int* seq_start, const int* seq_row0, void* out, float* partial, const float* sink, int rows,
+    int n_heads, int kw, float scale, int window, int splits, int rows_per_tile, void* stream) {
+    if (rows == 0) return 0;
+    SIB_REQUIRE(rows > 0 && sib_attention_latent_supports(n_heads, kw),
+                "attention_latent: rows=%d heads=%d row width=%d (a multiple of 16 up to 512)", rows,
+                n_heads, kw);
+    SIB_REQUIRE(k_new != nullptr || (k_pool && page_table && page_tokens > 0 && max_pages > 0),
+                "attention_latent: no keys given, or an incomplete cache description");
+    SIB_REQUIRE(splits >= 1 && splits < 65536 && (splits == 1 || partial != nullptr),
+                "attention_latent: splits=%d without scratch memory", splits);
+    SIB_REQUIRE(((uintptr_t)q % 16) == 0 && ((uintptr_t)k_new % 16) == 0 && ((uintptr_t)k_pool % 16) == 0 &&
+                    ((uintptr_t)out % 4) == 0,
+                "attention_latent: rows must start on 16-byte boundaries");
+    SIB_REQUIRE(window >= 0 && ring_tokens >= 0, "attention_latent: window=%d ring=%d", window, ring_tokens);
+    const int rpt = n_heads >= 16 ? 1 : (rows_per_tile < 1 ? 1 : (rows_per_tile * n_heads > 16 ? 16 / n_heads : rows_per_tile));
+    const int head_chunks = (n_heads + 15) / 16;
+    LatentArgs p{(const __nv_bfloat16*)q, (const __nv_bfloat16*)k_new, (const __nv_bfloat16*)k_pool,
+                 (__nv_bfloat16*)out, partial, sink, row_pos, row_seq, seq_slot, seq_start, seq_row0,
+                 page_table, rows, n_heads, kw, rpt, head_chunks, max_pages, page_tokens, ring_tokens,
+                 window, splits, scale};
+    const long long tiles = (long long)((rows + rpt - 1) / rpt) * head_chunks;
+    SIB_REQUIRE(tiles < (1ll << 31), "attention_latent: too many rows (%d)", rows);
+    const dim3 grid((unsigned)tiles, (unsigned)splits);
+    const size_t smem = (size_t)2 * KT * (kw + PADW) * sizeof(__nv_bfloat16) + (size_t)4 * 32 * 8 * sizeof(float);
+    cudaStream_t s = (cudaStream_t)stream;
+    if (kw <= 64) sib_launch_chained(latent_attention_kernel<1, 2>, grid, dim3(128), smem, s, p);
+    else if (kw <= 128) sib_launch_chained(latent_attention_kernel<2, 4>, grid, dim3(128), smem, s, p);
+    else if (kw <= 256) sib_launch_chained(latent_attention_kernel<4, 8>, grid, dim3(128), smem, s, p);
+    else sib_launch_chained(latent_attention_kernel<8, 16>, grid, dim3(128), smem, s, p);
+    int rc = sib_check_launch("attention_latent");
+    if (rc || splits == 1) return rc;
+    return sib_launch_attention_combine_sink_bf16((const float*)partial, out, rows * n_heads, splits, kw,
+                                                  sink, n_heads, s);
+}

@@ -311,6 +311,16 @@ int sib_launch_attention_combine_bf16(const float* partial, void* out, int units
     return sib_check_launch("attention_combine");
 }
 
+// Shared with attention_latent.cu: the same, with one sink per head in the denominator.
+int sib_launch_attention_combine_sink_bf16(const float* partial, void* out, int units, int splits,
+                                           int head_dim, const float* sink, int n_heads,
+                                           cudaStream_t s) {
+    const CombineShape c = combine_shape(splits, head_dim);
+    sib_launch_chained(attention_combine_kernel<__nv_bfloat16>, dim3(units), dim3(c.threads), c.smem,
+                       s, partial, (__nv_bfloat16*)out, splits, head_dim, c.groups, sink, n_heads);
+    return sib_check_launch("attention_combine");
+}
+
 SIB_EXPORT long long sib_attention_rows_scratch_bytes(int rows, int n_heads, int head_dim,
                                                       int splits) {
     if (splits <= 1) return 0;

@@ -841,6 +841,57 @@ def attention_rows(q: torch.Tensor, q_stride: int, k_new: Optional[torch.Tensor]
     return out
 
 
+def attention_latent_supports(n_heads: int, width: int) -> bool:
+    return bool(library().sib_attention_latent_supports(c_int(n_heads), c_int(width)))
+
+
+@_timed(lambda q, k_new, k_pool, page_table, page_tokens, ring_tokens, ctx, out, scratch, sink, n_heads,
+        width, scale, window, splits, rows_per_tile=1: (
+            _attention_cache_work("attention_latent (cache)", ctx.row_pos, k_pool, n_heads, width, window,
+                                  out.shape[0], value_dim=0) if k_new is None else
+            ("attention_latent (prompt)", _nbytes(q, k_new, out),
+             4.0 * float(((ctx.row_pos.to(torch.int64) + 1).clamp(max=window) if window
+                          else ctx.row_pos.to(torch.int64) + 1).sum().item()) * n_heads * width)))
+def attention_latent(q: torch.Tensor, k_new: Optional[torch.Tensor], k_pool: Optional[torch.Tensor],
+                     page_table: Optional[torch.Tensor], page_tokens: int, ring_tokens: int, ctx,
+                     out: torch.Tensor, scratch: Optional[torch.Tensor], sink: Optional[torch.Tensor],
+                     n_heads: int, width: int, scale: float, window: int, splits: int,
+                     rows_per_tile: int = 1) -> torch.Tensor:
+    """bfloat16 attention of every head over ONE shared row per position, on the tensor
+    cores (csrc/attention_latent.cu): ``q`` and ``out`` ``[rows, heads * width]``, keys (which
+    are the values too) from the step's rows ``k_new`` ``[rows, width]`` or from the cache
+    ``k_pool`` ``[pages, 1, page_tokens, width]``; ``sink`` one 32-bit value per head."""
+    rows = out.shape[0]
+    _want(q, torch.bfloat16, "q")
+    _want(out, torch.bfloat16, "out")
+    if tuple(q.shape) != (rows, n_heads * width) or tuple(out.shape) != (rows, n_heads * width):
+        raise KernelError("attention_latent: q and out must be [rows, heads * width]")
+    max_pages = 0
+    if k_new is not None:
+        _want(k_new, torch.bfloat16, "k_new")
+        if tuple(k_new.shape) != (rows, width):
+            raise KernelError("attention_latent: k_new must be [rows, width]")
+    else:
+        _want(k_pool, torch.bfloat16, "k_pool")
+        if tuple(k_pool.shape[1:]) != (1, page_tokens, width) or page_table is None:
+            raise KernelError("attention_latent: pool layout must be [pages, 1, page_tokens, width]")
+        max_pages = page_table.shape[1]
+    if splits > 1:
+        need = attention_rows_scratch_bytes(rows, n_heads, width, splits)
+        if scratch is None or scratch.numel() * scratch.element_size() < need:
+            raise KernelError(f"attention_latent: {need} bytes of scratch memory are needed")
+    if sink is not None:
+        _f32(sink, n_heads, "sink")
+    _check(library().sib_attention_latent(
+        _ptr(q), _ptr(k_new), _ptr(k_pool if k_new is None else None),
+        _ptr(page_table if k_new is None else None), c_int(max_pages), c_int(page_tokens),
+        c_int(ring_tokens), _ptr(ctx.row_pos), _ptr(ctx.row_seq), _ptr(ctx.seq_slot),
+        _ptr(ctx.seq_start), _ptr(ctx.seq_row0), _ptr(out), _ptr(scratch), _ptr(sink), c_int(rows),
+        c_int(n_heads), c_int(width), c_float(scale), c_int(window), c_int(splits),
+        c_int(rows_per_tile), _stream()))
+    return out
+
+
 def attention_decode_supports(n_heads: int, n_kv: int, head_dim: int, page_tokens: int) -> bool:
     return bool(library().sib_attention_decode_supports(c_int(n_heads), c_int(n_kv),
                                                         c_int(head_dim), c_int(page_tokens)))

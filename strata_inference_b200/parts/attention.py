@@ -62,6 +62,9 @@ from .registry import part_class, register_mixer
 _WARPS_PER_SM = 16
 # SIB_PREFILL_TCGEN05=0 selects the mma.sync prompt kernel instead of the tcgen05 one
 _USE_TCGEN05_PREFILL = os.environ.get("SIB_PREFILL_TCGEN05", "1") != "0"
+# SIB_LATENT_MMA=0 sends the bfloat16 latent attention to the general kernel instead of the
+# tensor-core one
+_USE_LATENT_MMA = os.environ.get("SIB_LATENT_MMA", "1") != "0"
 
 
 def decode_shape(units: int, longest: int, window: int, resident4: int, resident8: int,
@@ -473,8 +476,9 @@ class LatentAttention:
     The scores are taken against the cached rows themselves: <a_h, U_h c> = <U_h^T a_h, c>, so
     a query head becomes [U_h^T a_h | rot(r_h)], every head attends over the ONE row
     [c | rot(k_r)] per position, the weighted sum of the c rows comes out of the attention
-    kernel, and V_h is applied to that sum (csrc/head_prepare.cu latent_prepare,
-    csrc/attention_rows.cu with ``values_in_keys``).  The two per-head products are batched
+    kernel, and V_h is applied to that sum (csrc/head_prepare.cu latent_prepare; bfloat16:
+    csrc/attention_latent.cu, a key tile fetched once for all heads and used on the tensor
+    cores for scores and sums; 32-bit: csrc/attention_rows.cu with ``values_in_keys``).  The two per-head products are batched
     library products; softmax, sink and sums are 32-bit.
     """
 
@@ -568,6 +572,16 @@ class LatentAttention:
         want = max(1, self._target_warps // max(1, ctx.n_rows * self.nh))
         return max(1, min(want, -(-longest // 32), 128))
 
+    def _tile_splits(self, ctx, capacity: int) -> int:
+        """Runs of keys a tile of the tensor-core kernel (one row's heads, 16 at a time) is
+        cut into: as many as give every SM two blocks, none shorter than 64 keys."""
+        longest = (min(ctx.span or capacity, capacity)) if ctx.graph_capture else ctx.max_end
+        if self.window > 0:
+            longest = min(longest, self.window)
+        tiles = ctx.n_rows * (-(-self.nh // 16))
+        want = max(1, (2 * self.rt.sm_count) // max(1, tiles))
+        return max(1, min(want, -(-longest // 64), 128))
+
     def forward(self, x: torch.Tensor, ctx, entry: int, cache_entry: int,
                 owns_cache: bool) -> torch.Tensor:
         if not owns_cache:
@@ -598,7 +612,21 @@ class LatentAttention:
                               self.rot, ctx, view.k, view.page_table, view.page_tokens,
                               view.ring_tokens, nh, qd, rd, rank, kw)
         out = torch.empty((R, nh * kw), dtype=proj.dtype, device=proj.device)
-        if fresh:
+        tensor_cores = (proj.dtype == torch.bfloat16 and _USE_LATENT_MMA
+                        and native.attention_latent_supports(nh, kw))
+        if fresh and tensor_cores:
+            native.attention_latent(q_rows, k_rows, None, None, view.page_tokens, view.ring_tokens, ctx,
+                                    out, None, self.sink, nh, kw, self.scale, self.window, 1,
+                                    rows_per_tile=max(1, 16 // nh))
+        elif tensor_cores:
+            splits = self._tile_splits(ctx, ctx.cache.max_seq_len)
+            scratch = None
+            if splits > 1:
+                scratch = rt.scratch(native.attention_rows_scratch_bytes(R, nh, kw, splits))
+            native.attention_latent(q_rows, None, view.k, view.page_table, view.page_tokens,
+                                    view.ring_tokens, ctx, out, scratch, self.sink, nh, kw, self.scale,
+                                    self.window, splits)
+        elif fresh:
             native.attention_rows(q_rows, nh * kw, k_rows, k_rows, kw, None, None, None,
                                   view.page_tokens, view.ring_tokens, ctx.row_pos, ctx.row_seq,
                                   ctx.seq_slot, ctx.seq_start, ctx.seq_row0, out, None, nh, 1, kw,

@@ -8,6 +8,7 @@ from __future__ import annotations
 
 import copy
 import json
+import math
 import os
 import subprocess
 import sys
@@ -405,3 +406,69 @@ def test_relu_squared_feed_forward_alone(rows):
     got = part.forward(x.cuda(), None).float().cpu().double()
     ref = torch.from_numpy(plain.dense_ff(plain.f64(x.float()), {n.split("_")[0]: plain.f64(t.float()) for n, t in stored.items()}))
     assert (got - ref).abs().max().item() <= 2e-2 * ref.abs().max().item()
+
+
+def _latent_reference(q, keys_of, row_seq, row_pos, sink, scale, window):
+    """64-bit: every head of every row over its sequence's rows (keys that are values too)."""
+    rows, heads, kw = q.shape
+    out = torch.zeros((rows, heads, kw), dtype=torch.float64)
+    for r in range(rows):
+        c = keys_of[row_seq[r]].double()
+        p = row_pos[r]
+        lo = max(0, p - window + 1) if window else 0
+        for h in range(heads):
+            s = (c[lo:p + 1] @ q[r, h].double()) * scale
+            top = max(s.max().item(), sink[h].item())
+            e = torch.exp(s - top)
+            out[r, h] = (e @ c[lo:p + 1]) / (e.sum() + math.exp(sink[h].item() - top))
+    return out
+
+
+@pytest.mark.parametrize("heads, kw, window", [(16, 512, 0), (6, 112, 96), (3, 48, 17), (20, 64, 40),
+                                               (1, 16, 5), (8, 256, 300)])
+def test_tensor_core_latent_attention_alone(heads, kw, window):
+    """The bfloat16 kernel against a 64-bit sum over the same bfloat16 rows: prompts of unequal
+    lengths in one step (rows of a tile from two sequences), then single rows over a paged
+    cache whose pages lie in any order, whole and cut into runs of keys."""
+    from types import SimpleNamespace
+    from strata_inference_b200.kernels import native
+    g = torch.Generator().manual_seed(heads * 1000 + kw)
+    lens = [37, 1, 150, 5]
+    scale = 2.0 / math.sqrt(kw)
+    keys_of = [(torch.randn((n, kw), generator=g)).to(torch.bfloat16) for n in lens]
+    sink = torch.randn(heads, generator=g)
+    dev = lambda v: torch.tensor(v, dtype=torch.int32).cuda()  # noqa: E731
+    # prompts
+    rows = sum(lens)
+    row_seq = [b for b, n in enumerate(lens) for _ in range(n)]
+    row_pos = [i for n in lens for i in range(n)]
+    row0 = [sum(lens[:b]) for b in range(len(lens))]
+    q = torch.randn((rows, heads, kw), generator=g).to(torch.bfloat16)
+    ctx = SimpleNamespace(row_pos=dev(row_pos), row_seq=dev(row_seq), seq_slot=dev([0, 1, 2, 3]),
+                          seq_start=dev([0] * 4), seq_row0=dev(row0), n_seqs=4)
+    out = torch.empty((rows, heads * kw), dtype=torch.bfloat16, device="cuda")
+    native.attention_latent(q.reshape(rows, -1).cuda(), torch.cat(keys_of).cuda(), None, None, 16, 0, ctx, out,
+                            None, sink.cuda(), heads, kw, scale, window, 1, rows_per_tile=max(1, 16 // heads))
+    ref = _latent_reference(q, keys_of, row_seq, row_pos, sink, scale, window)
+    err = (out.cpu().double().view(rows, heads, kw) - ref).abs().max().item()
+    assert err <= 2e-2 * ref.abs().max().item(), f"prompts: {err:.3e} of {ref.abs().max().item():.3e}"
+    # single rows over the cache: sequence b's position j lies in page table[b][j // 16], cell j % 16
+    page_tokens, max_pages = 16, 10
+    order = torch.randperm(4 * max_pages, generator=g).view(4, max_pages)
+    pool = torch.zeros((4 * max_pages, 1, page_tokens, kw), dtype=torch.bfloat16)
+    for b, c in enumerate(keys_of):
+        for j in range(c.shape[0]):
+            pool[order[b, j // page_tokens], 0, j % page_tokens] = c[j]
+    last = [n - 1 for n in lens]
+    q1 = torch.randn((4, heads, kw), generator=g).to(torch.bfloat16)
+    ctx = SimpleNamespace(row_pos=dev(last), row_seq=dev([0, 1, 2, 3]), seq_slot=dev([0, 1, 2, 3]),
+                          seq_start=dev(last), seq_row0=dev([0, 1, 2, 3]), n_seqs=4)
+    ref = _latent_reference(q1, keys_of, [0, 1, 2, 3], last, sink, scale, window)
+    for splits in (1, 3, 7):
+        out = torch.empty((4, heads * kw), dtype=torch.bfloat16, device="cuda")
+        scratch = torch.empty(native.attention_rows_scratch_bytes(4, heads, kw, splits) + 16, dtype=torch.uint8,
+                              device="cuda") if splits > 1 else None
+        native.attention_latent(q1.reshape(4, -1).cuda(), None, pool.cuda(), order.to(torch.int32).cuda(),
+                                page_tokens, 0, ctx, out, scratch, sink.cuda(), heads, kw, scale, window, splits)
+        err = (out.cpu().double().view(4, heads, kw) - ref).abs().max().item()
+        assert err <= 2e-2 * ref.abs().max().item(), f"cache, {splits} runs: {err:.3e}"
