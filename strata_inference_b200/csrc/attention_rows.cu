@@ -1,5 +1,5 @@
 // Attention of independent query rows over the paged cache and the step's
-// own keys: the general kernel (any head size in steps of 16 up to 512, any
+// own keys: the general kernel (any head size in steps of 16 up to 1024, any
 // grouping, 32-bit or bfloat16 storage, 32-bit arithmetic throughout).
 //
 // For the query row at absolute position p of sequence b and query head h
@@ -337,8 +337,8 @@ SIB_EXPORT int sib_attention_rows(
     if (rows == 0) return 0;
     SIB_REQUIRE(rows > 0 && n_heads > 0 && n_kv > 0 && n_heads % n_kv == 0,
                 "attention_rows: rows=%d heads=%d kv_heads=%d", rows, n_heads, n_kv);
-    SIB_REQUIRE(head_dim >= 16 && head_dim % 16 == 0 && head_dim <= 512,
-                "attention_rows: head_dim=%d must be a multiple of 16 between 16 and 512", head_dim);
+    SIB_REQUIRE(head_dim >= 16 && head_dim % 16 == 0 && head_dim <= 1024,
+                "attention_rows: head_dim=%d must be a multiple of 16 between 16 and 1024", head_dim);
     SIB_REQUIRE(splits >= 1 && (splits == 1 || partial != nullptr),
                 "attention_rows: splits=%d without scratch memory", splits);
     SIB_REQUIRE((k_new != nullptr) == (v_new != nullptr) && (k_pool != nullptr) == (v_pool != nullptr),
@@ -369,7 +369,8 @@ SIB_EXPORT int sib_attention_rows(
     SIB_DISPATCH_DTYPE(dtype, {
         if (ni == 1) LAUNCH(1);
         else if (ni == 2) LAUNCH(2);
-        else LAUNCH(4);
+        else if (ni <= 4) LAUNCH(4);
+        else if constexpr (sizeof(T) == 4) LAUNCH(8);      // (32-bit rows wider than 512)
     });
 #undef LAUNCH
     int rc = sib_check_launch("attention_rows");

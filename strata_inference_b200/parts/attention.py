@@ -491,8 +491,8 @@ class LatentAttention:
         if min(nh, qd, vd, rank) <= 0 or rd < 0:
             raise ConfigError(f"latent_attention: {nh} heads of {qd} + {rd}, values of {vd}, rank {rank}")
         pad = -(-(rank + rd) // 16) * 16
-        if pad > 512:
-            raise ConfigError(f"latent_attention: kv_rank + rot_dim = {rank + rd} exceeds 512")
+        if pad > 1024:
+            raise ConfigError(f"latent_attention: kv_rank + rot_dim = {rank + rd} exceeds 1024")
         return nh, qd, rd, vd, rank, pad
 
     @classmethod

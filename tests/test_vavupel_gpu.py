@@ -17,7 +17,7 @@ import pytest
 import torch
 
 import plain_vavupel as plain
-from vavupel_cases import (ALONE, MIXED, NARROW, ODD, SHARP, STRAIGHT, WIDE, assert_close, plain_logits, prompts,
+from vavupel_cases import (ALONE, BROAD, MIXED, NARROW, ODD, SHARP, STRAIGHT, WIDE, assert_close, plain_logits, prompts,
                            random_weights, rows_that_differ)
 
 pytestmark = pytest.mark.gpu
@@ -241,9 +241,9 @@ def test_first_tokens_and_the_previous_token_across_steps():
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("name", ["odd", "wide", "narrow", "straight"])
+@pytest.mark.parametrize("name", ["odd", "wide", "narrow", "straight", "broad"])
 def test_other_sizes(name, dtype):
-    cfg = {"odd": ODD, "wide": WIDE, "narrow": NARROW, "straight": STRAIGHT}[name]
+    cfg = {"odd": ODD, "wide": WIDE, "narrow": NARROW, "straight": STRAIGHT, "broad": BROAD}[name]
     w = random_weights(cfg, seed=16)
     eng = make_engine(cfg, w, dtype)
     a, b = prompts(cfg, [150, 37], seed=17)

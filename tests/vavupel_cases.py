@@ -81,6 +81,9 @@ WIDE = model(128, 300, [
     retention(1, 320, 16, [0.995], rot_dims=100),
 ], loop=(0, 2, 2))
 
+# a latent row wider than 512 (the general attention kernel in both compute types)
+BROAD = model(64, 100, [latent(2, 16, 32, 16, 560, 50, ff=32), retention(1, 16, 16, [0.99])])
+
 # no loop at all
 STRAIGHT = model(64, 150, [retention(2, 16, 16, [0.9, 0.99], ff=32), latent(2, 16, 8, 16, 24, 30, ff=32)])
 
