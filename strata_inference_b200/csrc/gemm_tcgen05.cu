@@ -23,7 +23,8 @@
 
 #include "common.cuh"
 
-enum { GEMM_EPI_NONE = 0, GEMM_EPI_SOFTCAP = 1, GEMM_EPI_GEGLU = 2, GEMM_EPI_SWIGLU = 4 };
+enum { GEMM_EPI_NONE = 0, GEMM_EPI_SOFTCAP = 1, GEMM_EPI_GEGLU = 2, GEMM_EPI_SWIGLU = 4,
+       GEMM_EPI_RELU2 = 5 };    // (5: the square of max(y, 0), value by value)
 
 static constexpr int BM = 128;        // weight rows per block
 static constexpr int BK = 64;         // k per stage: 128 bytes, one swizzle row
@@ -231,6 +232,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
                     for (int j = 0; j < 32; ++j) {
                         float o = __uint_as_float(v[j]);
                         if (p.epilogue == GEMM_EPI_SOFTCAP) o = p.cap * tanhf(o / p.cap);
+                        if (p.epilogue == GEMM_EPI_RELU2) { o = fmaxf(o, 0.f); o *= o; }
                         const int r = r0 + c0 + j;
                         if (n < p.N && r < p.R) y[(size_t)r * p.y_stride + n] = from_f32<OutT>(o);
                     }
@@ -504,6 +506,7 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid
                     for (int j = 0; j < 32; ++j) {
                         o[j] = __uint_as_float(v[j]);
                         if (p.epilogue == GEMM_EPI_SOFTCAP) o[j] = p.cap * tanhf(o[j] / p.cap);
+                        if (p.epilogue == GEMM_EPI_RELU2) { o[j] = fmaxf(o[j], 0.f); o[j] *= o[j]; }
                     }
                     store_run<OutT>(y + (size_t)r * p.y_stride + n, o, min(32, p.N - n));
                 }

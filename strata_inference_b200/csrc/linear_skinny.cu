@@ -33,7 +33,8 @@
 
 namespace cg = cooperative_groups;
 
-enum { EPI_NONE = 0, EPI_SOFTCAP = 1, EPI_GEGLU = 2, EPI_ROPE = 3, EPI_SWIGLU = 4 };
+enum { EPI_NONE = 0, EPI_SOFTCAP = 1, EPI_GEGLU = 2, EPI_ROPE = 3, EPI_SWIGLU = 4,
+       EPI_RELU2 = 5 };     // (5: the square of max(y, 0), value by value)
 
 // What the q|k|v product needs to rotate and store (see rope_cache.cu for the cache layout).
 struct RopeTail {
@@ -270,6 +271,10 @@ __device__ __forceinline__ void skinny_linear_body(
 #pragma unroll
                 for (int c = 0; c < 4; ++c) o[c] = cap * tanhf(o[c] / cap);
             }
+            if (EPI == EPI_RELU2) {
+#pragma unroll
+                for (int c = 0; c < 4; ++c) { const float t = fmaxf(o[c], 0.f); o[c] = t * t; }
+            }
 #pragma unroll
             for (int c = 0; c < 4; ++c) {
                 const int n = n_lo + (c >= 2 ? 8 : 0), r = r0 + (c & 1);
@@ -407,6 +412,7 @@ SIB_EXPORT int sib_skinny_linear(const void* W, const void* x, void* y, int out_
         if (epilogue == EPI_GEGLU) GO(__nv_bfloat16, EPI_GEGLU);
         if (epilogue == EPI_SWIGLU) GO(__nv_bfloat16, EPI_SWIGLU);
         if (epilogue == EPI_SOFTCAP) GO(__nv_bfloat16, EPI_SOFTCAP);
+        if (epilogue == EPI_RELU2) GO(__nv_bfloat16, EPI_RELU2);
     } else if (out_dtype == SIB_F32) {
         if (epilogue == EPI_NONE) GO(float, EPI_NONE);
         if (epilogue == EPI_SOFTCAP) GO(float, EPI_SOFTCAP);

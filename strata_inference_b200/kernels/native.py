@@ -20,6 +20,7 @@ import torch
 F32, BF16 = 0, 1
 EPI_NONE, EPI_SOFTCAP, EPI_GEGLU = 0, 1, 2
 EPI_SWIGLU = 4          # the gated epilogue with SiLU (weight-streaming and paired tcgen05 products)
+EPI_RELU2 = 5           # the square of max(y, 0), value by value (the same two products)
 GATED_EPILOGUES = (EPI_GEGLU, EPI_SWIGLU)
 ROPE_HALF_SPLIT, ROPE_INTERLEAVED = 0, 1
 ACT_GELU_TANH, ACT_SILU = 0, 1          # of the gated feed-forward

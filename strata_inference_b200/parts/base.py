@@ -103,6 +103,10 @@ class Runtime:
         # from this many rows on the gate/up product with its gated epilogue (pairs of SMs,
         # 256 x 256 tiles) beats the library product followed by the activation kernel
         self.gated_gemm_min_rows = 128
+        # SIB_RELU2_GEMM=0: many rows of a feed-forward without a gate take the library product
+        # and the activation kernel instead of the tcgen05 product with the activation in its
+        # epilogue
+        self.fuse_relu2_gemm = os.environ.get("SIB_RELU2_GEMM", "1") != "0"
         # SIB_EARLY_KEYS=0: the attention over the cache fetches no keys before the kernel ahead
         # of it has finished
         self.early_keys = os.environ.get("SIB_EARLY_KEYS", "1") != "0"
@@ -203,7 +207,7 @@ class Runtime:
         n_out = N // 2 if gated else N
         # (the chain kernel, the staged product and the tcgen05 weight-streaming product know
         # the tanh-GELU gate only)
-        only_gelu = epilogue != native.EPI_SWIGLU
+        only_gelu = epilogue not in (native.EPI_SWIGLU, native.EPI_RELU2)
         if self._chainable(x, w, out_dtype) and only_gelu and (out_dtype == torch.bfloat16
                                                                or not gated):
             out = torch.empty((R, n_out), dtype=out_dtype, device=x.device)
@@ -226,7 +230,8 @@ class Runtime:
             # the weight-streaming tcgen05 product, with its epilogue
             out = torch.empty((R, n_out), dtype=out_dtype, device=x.device)
             return native.linear_rows_tc(x, w, out, epilogue, cap)
-        fused_gate = gated and R > self.gated_gemm_min_rows
+        fused_gate = (gated or (epilogue == native.EPI_RELU2 and self.fuse_relu2_gemm)) \
+            and R > self.gated_gemm_min_rows
         if x.dtype == torch.bfloat16 and aligned and (out_dtype == torch.float32 or fused_gate):
             # the tcgen05 product where its epilogue saves a pass over the outputs: 32-bit
             # logits of many rows, soft-capped as they are written; the gated activation of
@@ -246,6 +251,8 @@ class Runtime:
             if y.dtype != torch.float32:
                 raise ValueError("the soft cap epilogue is applied to 32-bit outputs")
             native.softcap_(y, cap)
+        elif epilogue == native.EPI_RELU2:
+            native.activate(y, y, native.ACT_RELU_SQUARED)
         return y
 
 

@@ -118,8 +118,13 @@ class PlainMLP:
         self.w_down = rt.cast_matrix(weights["down_proj.weight"])
 
     def forward(self, x: torch.Tensor, ctx) -> torch.Tensor:
-        up = self.rt.linear(x, self.w_up)
-        native.activate(up, up, self.act)
+        if self.act == native.ACT_RELU_SQUARED:
+            # (the products have this activation as an epilogue; where a library product is
+            # taken the runtime applies it behind)
+            up = self.rt.linear(x, self.w_up, epilogue=native.EPI_RELU2)
+        else:
+            up = self.rt.linear(x, self.w_up)
+            native.activate(up, up, self.act)
         return self.rt.linear(up, self.w_down)
 
 
