@@ -8,7 +8,8 @@
 //     out[r, h, :] = (sum_j e^{s_j - M} c_j) / (sum_j e^{s_j - M} + e^{sink_h - M})
 // every head reads the same rows, so a block takes a tile of up to 16 (row, head) pairs as the
 // M side of mma.sync.m16n8k16 and walks the keys 16 at a time: a key tile is fetched ONCE
-// (cp.async, two buffers in turn) and serves all heads as the B operand of the scores
+// (cp.async, three buffers in turn: two tiles are on their way while one is worked on) and
+// serves all heads as the B operand of the scores
 // (S = Q C^T, the block's 4 warps split kw and add their parts through shared memory) and,
 // transposed by ldmatrix, of the weighted sum (O += P C, the warps split the columns).  A tile
 // holds 16 heads of one row, or with fewer than 16 heads the heads of several consecutive
@@ -49,6 +50,7 @@ struct LatentArgs {
 };
 
 constexpr int KT = 16;             // keys of a tile
+constexpr int STAGES = 3;          // staged tiles
 constexpr int PADW = 8;            // bfloat16 elements between the rows of a staged tile
 
 __device__ __forceinline__ void cp16(void* smem, const void* gmem, bool valid) {
@@ -72,6 +74,12 @@ __device__ __forceinline__ void mma16816(float (&c)[4], const uint32_t (&a)[4], 
         : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
         : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
 }
+// 2^x on the special-function unit (relative error about 2^-22; 2^-inf = 0)
+__device__ __forceinline__ float exp2_fast(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;\n" : "=f"(y) : "f"(x));
+    return y;
+}
 __device__ __forceinline__ uint32_t pack2(float lo, float hi) {
     const __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
     return *reinterpret_cast<const uint32_t*>(&v);
@@ -85,8 +93,8 @@ __global__ void __launch_bounds__(128) latent_attention_kernel(LatentArgs p) {
     pdl_trigger();
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int kw = p.kw, ldk = kw + PADW;
-    __nv_bfloat16* tiles = reinterpret_cast<__nv_bfloat16*>(smem_raw);           // [2][KT][ldk]
-    float* red = reinterpret_cast<float*>(smem_raw + (size_t)2 * KT * ldk * sizeof(__nv_bfloat16));  // [4][32][8]
+    __nv_bfloat16* tiles = reinterpret_cast<__nv_bfloat16*>(smem_raw);           // [STAGES][KT][ldk]
+    float* red = reinterpret_cast<float*>(smem_raw + (size_t)STAGES * KT * ldk * sizeof(__nv_bfloat16));  // [4][32][8]
     const int n_ksteps = kw / 16, n_ntiles = kw / 8;
     const int chunk = blockIdx.x % p.head_chunks;
     const int r0 = (blockIdx.x / p.head_chunks) * p.rpt;
@@ -130,6 +138,9 @@ __global__ void __launch_bounds__(128) latent_attention_kernel(LatentArgs p) {
     for (int t = 0; t < NT; ++t)
 #pragma unroll
         for (int e = 0; e < 4; ++e) o[t][e] = 0.f;
+    // (scores, maxima and the sink in units of log 2, so that a weight is one 2^x)
+    constexpr float LOG2E = 1.4426950408889634f;
+    const float scale2 = p.scale * LOG2E;
     float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};
 
     // one sequence's rows of the tile after the other
@@ -158,32 +169,45 @@ __global__ void __launch_bounds__(128) latent_attention_kernel(LatentArgs p) {
         }
         const int n_tiles = j1 > j0 ? (j1 - j0 + KT - 1) / KT : 0;
         const int chunks_per_key = kw / 8;
-        auto fetch = [&](int t) {
-            __nv_bfloat16* dst = tiles + (size_t)(t & 1) * KT * ldk;
-            for (int c = tid; c < KT * chunks_per_key; c += 128) {
-                const int key = c / chunks_per_key, part = c - key * chunks_per_key;
-                const int j = j0 + t * KT + key;
-                const bool valid = j < j1;
-                const __nv_bfloat16* src = p.q;      // (any valid address: nothing is read when !valid)
-                if (valid) {
-                    if (p.k_new && j >= start) {
-                        src = p.k_new + (size_t)(row0 + (j - start)) * kw;
-                    } else {
-                        const int cell = p.ring_tokens > 0 ? j % p.ring_tokens : j;
-                        const int page = p.page_table[(size_t)slot * p.max_pages + cell / p.page_tokens];
-                        src = p.k_pool + ((size_t)page * p.page_tokens + cell % p.page_tokens) * kw;
-                    }
-                    src += part * 8;
-                }
-                cp16(dst + (size_t)key * ldk + part * 8, src, valid);
+        // Where a tile's 16 rows lie: lane l (and l + 16) of every warp looks up row l, one
+        // tile ahead of the fetch that uses it, so that the page table's answer has come by
+        // then; the lanes then hand the addresses to whichever lane copies a piece of the row.
+        auto key_src = [&](int t) -> const __nv_bfloat16* {
+            const int j = j0 + t * KT + (lane & 15);
+            if (t >= n_tiles || j >= j1) return nullptr;
+            if (p.k_new && j >= start) return p.k_new + (size_t)(row0 + (j - start)) * kw;
+            const int cell = p.ring_tokens > 0 ? j % p.ring_tokens : j;
+            const int page = p.page_table[(size_t)slot * p.max_pages + cell / p.page_tokens];
+            return p.k_pool + ((size_t)page * p.page_tokens + cell % p.page_tokens) * kw;
+        };
+        const __nv_bfloat16* src_next = key_src(0);
+        const int pieces = KT * chunks_per_key;
+        const int step_key = 128 / chunks_per_key, step_part = 128 % chunks_per_key;
+        auto fetch = [&](int t) {          // (called for t = 0, 1, 2, ... in this order)
+            __nv_bfloat16* dst = tiles + (size_t)(t % STAGES) * KT * ldk;
+            const __nv_bfloat16* src_mine = src_next;
+            src_next = key_src(t + 1);
+            int key = tid / chunks_per_key, part = tid % chunks_per_key;
+            for (int c0 = 0; c0 < pieces; c0 += 128) {
+                const bool inside = c0 + tid < pieces;
+                const __nv_bfloat16* src = reinterpret_cast<const __nv_bfloat16*>(
+                    __shfl_sync(0xffffffffu, reinterpret_cast<unsigned long long>(src_mine), inside ? key : 0));
+                if (inside)      // (a row beyond the run's end is filled with zeros)
+                    cp16(dst + (size_t)key * ldk + part * 8, src ? src + part * 8 : p.q, src != nullptr);
+                key += step_key;
+                part += step_part;
+                if (part >= chunks_per_key) { part -= chunks_per_key; ++key; }
             }
             cp_commit();
         };
         if (n_tiles > 0) fetch(0);
+        if (n_tiles > 1) fetch(1);
         for (int t = 0; t < n_tiles; ++t) {
-            if (t + 1 < n_tiles) { fetch(t + 1); cp_wait<1>(); } else { cp_wait<0>(); }
+            if (t + 2 < n_tiles) { fetch(t + 2); cp_wait<2>(); }
+            else if (t + 1 < n_tiles) { cp_wait<1>(); }
+            else { cp_wait<0>(); }
             __syncthreads();
-            const __nv_bfloat16* kt = tiles + (size_t)(t & 1) * KT * ldk;
+            const __nv_bfloat16* kt = tiles + (size_t)(t % STAGES) * KT * ldk;
             // this warp's part of the scores: 16 units x 16 keys
             float s[2][4];
 #pragma unroll
@@ -202,29 +226,39 @@ __global__ void __launch_bounds__(128) latent_attention_kernel(LatentArgs p) {
                     }
                 }
             }
-            float* mine = red + ((size_t)warp * 32 + lane) * 8;
+            // (value-major, so that the lanes of a warp touch neighbouring words)
 #pragma unroll
             for (int n = 0; n < 2; ++n)
 #pragma unroll
-                for (int e = 0; e < 4; ++e) mine[n * 4 + e] = s[n][e];
+                for (int e = 0; e < 4; ++e) red[(warp * 8 + n * 4 + e) * 32 + lane] = s[n][e];
             __syncthreads();
 #pragma unroll
             for (int n = 0; n < 2; ++n)
 #pragma unroll
                 for (int e = 0; e < 4; ++e)
-                    s[n][e] = (red[(0 * 32 + lane) * 8 + n * 4 + e] + red[(1 * 32 + lane) * 8 + n * 4 + e]) +
-                              (red[(2 * 32 + lane) * 8 + n * 4 + e] + red[(3 * 32 + lane) * 8 + n * 4 + e]);
-            // scale, mask, running maximum (per row of the M side: e = 0 holds s[n][0..1], e = 1 s[n][2..3])
+                    s[n][e] = (red[(0 * 8 + n * 4 + e) * 32 + lane] + red[(1 * 8 + n * 4 + e) * 32 + lane]) +
+                              (red[(2 * 8 + n * 4 + e) * 32 + lane] + red[(3 * 8 + n * 4 + e) * 32 + lane]);
+            // scale (to powers of two), mask, running maximum (per row of the M side: e = 0 holds
+            // s[n][0..1], e = 1 s[n][2..3]).  A tile that every row of the warp sees whole
+            // skips the mask (a row that is not stored at all may then hold anything finite).
             const int jt = j0 + t * KT;
+            bool plain = jt + KT <= j1;
+#pragma unroll
+            for (int r = 0; r < 2; ++r)
+                plain = plain && (!my_valid[r] || (act[r] && lo[r] <= jt && pos[r] >= jt + KT - 1));
+            plain = __all_sync(0xffffffffu, plain);
             float mx[2] = {-INFINITY, -INFINITY};
 #pragma unroll
             for (int n = 0; n < 2; ++n)
 #pragma unroll
                 for (int e = 0; e < 4; ++e) {
                     const int r = e >> 1;
-                    const int j = jt + n * 8 + 2 * q4 + (e & 1);
-                    const bool see = act[r] && j >= lo[r] && j <= pos[r] && j < j1;
-                    s[n][e] = see ? s[n][e] * p.scale : -INFINITY;
+                    bool see = true;
+                    if (!plain) {
+                        const int j = jt + n * 8 + 2 * q4 + (e & 1);
+                        see = act[r] && j >= lo[r] && j <= pos[r] && j < j1;
+                    }
+                    s[n][e] = see ? s[n][e] * scale2 : -INFINITY;
                     mx[r] = fmaxf(mx[r], s[n][e]);
                 }
             float corr[2];
@@ -233,7 +267,7 @@ __global__ void __launch_bounds__(128) latent_attention_kernel(LatentArgs p) {
                 mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 1));
                 mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 2));
                 const float m_new = fmaxf(m_run[r], mx[r]);
-                corr[r] = m_new == -INFINITY ? 1.f : expf(m_run[r] - m_new);    // (-inf - finite: 0)
+                corr[r] = m_new == -INFINITY ? 1.f : exp2_fast(m_run[r] - m_new);    // (-inf - finite: 0)
                 m_run[r] = m_new;
                 l_run[r] *= corr[r];
             }
@@ -243,9 +277,10 @@ __global__ void __launch_bounds__(128) latent_attention_kernel(LatentArgs p) {
 #pragma unroll
                 for (int e = 0; e < 4; ++e) {
                     const int r = e >> 1;
-                    pr[n][e] = s[n][e] == -INFINITY ? 0.f : expf(s[n][e] - m_run[r]);
+                    pr[n][e] = m_run[r] == -INFINITY ? 0.f : exp2_fast(s[n][e] - m_run[r]);
                     l_run[r] += pr[n][e];
                 }
+            const bool rescale = !__all_sync(0xffffffffu, corr[0] == 1.f && corr[1] == 1.f);
             uint32_t pa[4] = {pack2(pr[0][0], pr[0][1]), pack2(pr[0][2], pr[0][3]),
                               pack2(pr[1][0], pr[1][1]), pack2(pr[1][2], pr[1][3])};
             // the weighted sum of this warp's columns (tiles warp, warp + 4, ... of 8 columns)
@@ -253,14 +288,16 @@ __global__ void __launch_bounds__(128) latent_attention_kernel(LatentArgs p) {
             for (int ti = 0; ti < NT; ++ti) {
                 const int nt = warp + 4 * ti;
                 if (nt < n_ntiles) {
-                    o[ti][0] *= corr[0]; o[ti][1] *= corr[0];
-                    o[ti][2] *= corr[1]; o[ti][3] *= corr[1];
+                    if (rescale) {
+                        o[ti][0] *= corr[0]; o[ti][1] *= corr[0];
+                        o[ti][2] *= corr[1]; o[ti][3] *= corr[1];
+                    }
                     uint32_t b0, b1;
                     ldsm_x2_trans(b0, b1, kt + (size_t)(lane & 15) * ldk + nt * 8);
                     mma16816(o[ti], pa, b0, b1);
                 }
             }
-            __syncthreads();       // (the tile's buffer is fetched into again two tiles on)
+            __syncthreads();       // (the tile's buffer is fetched into again at the next tile's start)
         }
         done += cnt;
     }
@@ -276,10 +313,10 @@ __global__ void __launch_bounds__(128) latent_attention_kernel(LatentArgs p) {
         for (int r = 0; r < 2; ++r) {
             float scale_o = 1.f, l = l_run[r];
             if (p.sink && my_valid[r]) {
-                const float sk = p.sink[my_head[r]];
+                const float sk = p.sink[my_head[r]] * LOG2E;
                 const float top = fmaxf(m_run[r], sk);
-                scale_o = m_run[r] == -INFINITY ? 0.f : expf(m_run[r] - top);
-                l = l * scale_o + expf(sk - top);
+                scale_o = m_run[r] == -INFINITY ? 0.f : exp2_fast(m_run[r] - top);
+                l = l * scale_o + exp2_fast(sk - top);
             }
             inv[r] = l > 0.f ? scale_o / l : 0.f;
         }
@@ -299,7 +336,8 @@ __global__ void __launch_bounds__(128) latent_attention_kernel(LatentArgs p) {
         for (int r = 0; r < 2; ++r) {
             if (!my_valid[r]) continue;
             float* pp = p.partial + (((size_t)my_row[r] * p.n_heads + my_head[r]) * p.splits + split) * (kw + 2);
-            if (warp == 0 && q4 == 0) { pp[0] = m_run[r]; pp[1] = l_run[r]; }
+            // (the combine kernel takes maxima in natural units)
+            if (warp == 0 && q4 == 0) { pp[0] = m_run[r] * (1.0f / LOG2E); pp[1] = l_run[r]; }
 #pragma unroll
             for (int ti = 0; ti < NT; ++ti) {
                 const int nt = warp + 4 * ti;
@@ -342,12 +380,22 @@ SIB_EXPORT int sib_attention_latent(
     const long long tiles = (long long)((rows + rpt - 1) / rpt) * head_chunks;
     SIB_REQUIRE(tiles < (1ll << 31), "attention_latent: too many rows (%d)", rows);
     const dim3 grid((unsigned)tiles, (unsigned)splits);
-    const size_t smem = (size_t)2 * KT * (kw + PADW) * sizeof(__nv_bfloat16) + (size_t)4 * 32 * 8 * sizeof(float);
+    const size_t smem = (size_t)STAGES * KT * (kw + PADW) * sizeof(__nv_bfloat16) + (size_t)4 * 32 * 8 * sizeof(float);
     cudaStream_t s = (cudaStream_t)stream;
-    if (kw <= 64) sib_launch_chained(latent_attention_kernel<1, 2>, grid, dim3(128), smem, s, p);
-    else if (kw <= 128) sib_launch_chained(latent_attention_kernel<2, 4>, grid, dim3(128), smem, s, p);
-    else if (kw <= 256) sib_launch_chained(latent_attention_kernel<4, 8>, grid, dim3(128), smem, s, p);
-    else sib_launch_chained(latent_attention_kernel<8, 16>, grid, dim3(128), smem, s, p);
+#define GO(KSW, NT)                                                                                \
+    do {                                                                                           \
+        if (smem > 48 * 1024) {                                                                    \
+            cudaError_t e = cudaFuncSetAttribute(latent_attention_kernel<KSW, NT>,                 \
+                                                 cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
+            SIB_REQUIRE(e == cudaSuccess, "attention_latent: %s", cudaGetErrorString(e));          \
+        }                                                                                          \
+        sib_launch_chained(latent_attention_kernel<KSW, NT>, grid, dim3(128), smem, s, p);         \
+    } while (0)
+    if (kw <= 64) GO(1, 2);
+    else if (kw <= 128) GO(2, 4);
+    else if (kw <= 256) GO(4, 8);
+    else GO(8, 16);
+#undef GO
     int rc = sib_check_launch("attention_latent");
     if (rc || splits == 1) return rc;
     return sib_launch_attention_combine_sink_bf16((const float*)partial, out, rows * n_heads, splits, kw,
