@@ -7,8 +7,8 @@
 //     s_j = scale <q[r, h], c_j>,   visible j: max(0, p - window + 1) <= j <= p  (window 0: all)
 //     out[r, h, :] = (sum_j e^{s_j - M} c_j) / (sum_j e^{s_j - M} + e^{sink_h - M})
 // every head reads the same rows, so a block takes a tile of up to 16 (row, head) pairs as the
-// M side of mma.sync.m16n8k16 and walks the keys 16 at a time: a key tile is fetched ONCE
-// (cp.async, three buffers in turn: two tiles are on their way while one is worked on) and
+// M side of mma.sync.m16n8k16 and walks the keys 32 at a time: a key tile is fetched ONCE
+// (cp.async, two buffers in turn: the next tile is on its way while one is worked on) and
 // serves all heads as the B operand of the scores
 // (S = Q C^T, the block's 4 warps split kw and add their parts through shared memory) and,
 // transposed by ldmatrix, of the weighted sum (O += P C, the warps split the columns).  A tile
@@ -49,8 +49,11 @@ struct LatentArgs {
     float scale;
 };
 
-constexpr int KT = 16;             // keys of a tile
-constexpr int STAGES = 3;          // staged tiles
+constexpr int KT = 32;             // keys of a tile
+constexpr int NKT = KT / 8;        // the tile's groups of 8 keys (N side of the scores)
+constexpr int KKT = KT / 16;       // the tile's groups of 16 keys (K side of the weighted sum)
+static_assert(KT == 32, "a lane of a warp looks up one row of the tile");
+constexpr int STAGES = 2;          // staged tiles
 constexpr int PADW = 8;            // bfloat16 elements between the rows of a staged tile
 
 __device__ __forceinline__ void cp16(void* smem, const void* gmem, bool valid) {
@@ -94,7 +97,7 @@ __global__ void __launch_bounds__(128) latent_attention_kernel(LatentArgs p) {
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int kw = p.kw, ldk = kw + PADW;
     __nv_bfloat16* tiles = reinterpret_cast<__nv_bfloat16*>(smem_raw);           // [STAGES][KT][ldk]
-    float* red = reinterpret_cast<float*>(smem_raw + (size_t)STAGES * KT * ldk * sizeof(__nv_bfloat16));  // [4][32][8]
+    float* red = reinterpret_cast<float*>(smem_raw + (size_t)STAGES * KT * ldk * sizeof(__nv_bfloat16));  // [4][NKT * 4][32]
     const int n_ksteps = kw / 16, n_ntiles = kw / 8;
     const int chunk = blockIdx.x % p.head_chunks;
     const int r0 = (blockIdx.x / p.head_chunks) * p.rpt;
@@ -169,11 +172,11 @@ __global__ void __launch_bounds__(128) latent_attention_kernel(LatentArgs p) {
         }
         const int n_tiles = j1 > j0 ? (j1 - j0 + KT - 1) / KT : 0;
         const int chunks_per_key = kw / 8;
-        // Where a tile's 16 rows lie: lane l (and l + 16) of every warp looks up row l, one
+        // Where a tile's 32 rows lie: lane l of every warp looks up row l, one
         // tile ahead of the fetch that uses it, so that the page table's answer has come by
         // then; the lanes then hand the addresses to whichever lane copies a piece of the row.
         auto key_src = [&](int t) -> const __nv_bfloat16* {
-            const int j = j0 + t * KT + (lane & 15);
+            const int j = j0 + t * KT + (lane % KT);
             if (t >= n_tiles || j >= j1) return nullptr;
             if (p.k_new && j >= start) return p.k_new + (size_t)(row0 + (j - start)) * kw;
             const int cell = p.ring_tokens > 0 ? j % p.ring_tokens : j;
@@ -201,17 +204,15 @@ __global__ void __launch_bounds__(128) latent_attention_kernel(LatentArgs p) {
             cp_commit();
         };
         if (n_tiles > 0) fetch(0);
-        if (n_tiles > 1) fetch(1);
         for (int t = 0; t < n_tiles; ++t) {
-            if (t + 2 < n_tiles) { fetch(t + 2); cp_wait<2>(); }
-            else if (t + 1 < n_tiles) { cp_wait<1>(); }
+            if (t + 1 < n_tiles) { fetch(t + 1); cp_wait<1>(); }
             else { cp_wait<0>(); }
             __syncthreads();
             const __nv_bfloat16* kt = tiles + (size_t)(t % STAGES) * KT * ldk;
             // this warp's part of the scores: 16 units x 16 keys
-            float s[2][4];
+            float s[NKT][4];
 #pragma unroll
-            for (int n = 0; n < 2; ++n)
+            for (int n = 0; n < NKT; ++n)
 #pragma unroll
                 for (int e = 0; e < 4; ++e) s[n][e] = 0.f;
 #pragma unroll
@@ -219,7 +220,7 @@ __global__ void __launch_bounds__(128) latent_attention_kernel(LatentArgs p) {
                 const int ks = warp + 4 * sidx;
                 if (ks < n_ksteps) {
 #pragma unroll
-                    for (int n = 0; n < 2; ++n) {
+                    for (int n = 0; n < NKT; ++n) {
                         const __nv_bfloat16* bp = kt + (size_t)(n * 8 + g4) * ldk + ks * 16 + 2 * q4;
                         mma16816(s[n], qa[sidx], *reinterpret_cast<const uint32_t*>(bp),
                                  *reinterpret_cast<const uint32_t*>(bp + 8));
@@ -228,16 +229,16 @@ __global__ void __launch_bounds__(128) latent_attention_kernel(LatentArgs p) {
             }
             // (value-major, so that the lanes of a warp touch neighbouring words)
 #pragma unroll
-            for (int n = 0; n < 2; ++n)
+            for (int n = 0; n < NKT; ++n)
 #pragma unroll
-                for (int e = 0; e < 4; ++e) red[(warp * 8 + n * 4 + e) * 32 + lane] = s[n][e];
+                for (int e = 0; e < 4; ++e) red[(warp * NKT * 4 + n * 4 + e) * 32 + lane] = s[n][e];
             __syncthreads();
 #pragma unroll
-            for (int n = 0; n < 2; ++n)
+            for (int n = 0; n < NKT; ++n)
 #pragma unroll
                 for (int e = 0; e < 4; ++e)
-                    s[n][e] = (red[(0 * 8 + n * 4 + e) * 32 + lane] + red[(1 * 8 + n * 4 + e) * 32 + lane]) +
-                              (red[(2 * 8 + n * 4 + e) * 32 + lane] + red[(3 * 8 + n * 4 + e) * 32 + lane]);
+                    s[n][e] = (red[(0 * NKT * 4 + n * 4 + e) * 32 + lane] + red[(1 * NKT * 4 + n * 4 + e) * 32 + lane]) +
+                              (red[(2 * NKT * 4 + n * 4 + e) * 32 + lane] + red[(3 * NKT * 4 + n * 4 + e) * 32 + lane]);
             // scale (to powers of two), mask, running maximum (per row of the M side: e = 0 holds
             // s[n][0..1], e = 1 s[n][2..3]).  A tile that every row of the warp sees whole
             // skips the mask (a row that is not stored at all may then hold anything finite).
@@ -249,7 +250,7 @@ __global__ void __launch_bounds__(128) latent_attention_kernel(LatentArgs p) {
             plain = __all_sync(0xffffffffu, plain);
             float mx[2] = {-INFINITY, -INFINITY};
 #pragma unroll
-            for (int n = 0; n < 2; ++n)
+            for (int n = 0; n < NKT; ++n)
 #pragma unroll
                 for (int e = 0; e < 4; ++e) {
                     const int r = e >> 1;
@@ -271,9 +272,9 @@ __global__ void __launch_bounds__(128) latent_attention_kernel(LatentArgs p) {
                 m_run[r] = m_new;
                 l_run[r] *= corr[r];
             }
-            float pr[2][4];
+            float pr[NKT][4];
 #pragma unroll
-            for (int n = 0; n < 2; ++n)
+            for (int n = 0; n < NKT; ++n)
 #pragma unroll
                 for (int e = 0; e < 4; ++e) {
                     const int r = e >> 1;
@@ -281,8 +282,14 @@ __global__ void __launch_bounds__(128) latent_attention_kernel(LatentArgs p) {
                     l_run[r] += pr[n][e];
                 }
             const bool rescale = !__all_sync(0xffffffffu, corr[0] == 1.f && corr[1] == 1.f);
-            uint32_t pa[4] = {pack2(pr[0][0], pr[0][1]), pack2(pr[0][2], pr[0][3]),
-                              pack2(pr[1][0], pr[1][1]), pack2(pr[1][2], pr[1][3])};
+            uint32_t pa[KKT][4];
+#pragma unroll
+            for (int kk = 0; kk < KKT; ++kk) {
+                pa[kk][0] = pack2(pr[2 * kk][0], pr[2 * kk][1]);
+                pa[kk][1] = pack2(pr[2 * kk][2], pr[2 * kk][3]);
+                pa[kk][2] = pack2(pr[2 * kk + 1][0], pr[2 * kk + 1][1]);
+                pa[kk][3] = pack2(pr[2 * kk + 1][2], pr[2 * kk + 1][3]);
+            }
             // the weighted sum of this warp's columns (tiles warp, warp + 4, ... of 8 columns)
 #pragma unroll
             for (int ti = 0; ti < NT; ++ti) {
@@ -292,12 +299,15 @@ __global__ void __launch_bounds__(128) latent_attention_kernel(LatentArgs p) {
                         o[ti][0] *= corr[0]; o[ti][1] *= corr[0];
                         o[ti][2] *= corr[1]; o[ti][3] *= corr[1];
                     }
-                    uint32_t b0, b1;
-                    ldsm_x2_trans(b0, b1, kt + (size_t)(lane & 15) * ldk + nt * 8);
-                    mma16816(o[ti], pa, b0, b1);
+#pragma unroll
+                    for (int kk = 0; kk < KKT; ++kk) {
+                        uint32_t b0, b1;
+                        ldsm_x2_trans(b0, b1, kt + (size_t)(kk * 16 + (lane & 15)) * ldk + nt * 8);
+                        mma16816(o[ti], pa[kk], b0, b1);
+                    }
                 }
             }
-            __syncthreads();       // (the tile's buffer is fetched into again at the next tile's start)
+            __syncthreads();       // (the tile's buffer is fetched into again at the start of the tile after the next)
         }
         done += cnt;
     }
@@ -380,7 +390,7 @@ SIB_EXPORT int sib_attention_latent(
     const long long tiles = (long long)((rows + rpt - 1) / rpt) * head_chunks;
     SIB_REQUIRE(tiles < (1ll << 31), "attention_latent: too many rows (%d)", rows);
     const dim3 grid((unsigned)tiles, (unsigned)splits);
-    const size_t smem = (size_t)STAGES * KT * (kw + PADW) * sizeof(__nv_bfloat16) + (size_t)4 * 32 * 8 * sizeof(float);
+    const size_t smem = (size_t)STAGES * KT * (kw + PADW) * sizeof(__nv_bfloat16) + (size_t)4 * NKT * 4 * 32 * sizeof(float);
     cudaStream_t s = (cudaStream_t)stream;
 #define GO(KSW, NT)                                                                                \
     do {                                                                                           \
