@@ -523,6 +523,13 @@ def run_karupel(args, pair=None, title="Karupel beside Gemma2"):
             randomize_pools(engine)
             weight_bytes = engine.model.weight_bytes()
             row = {"weights_gb": round(weight_bytes / 1e9, 2)}
+            if getattr(engine.model.head, "weight", None) is not engine.model.embedding.table:
+                # (a model whose logits have a matrix of their own reads a few rows of its
+                # embedding tables in a step, not the tables)
+                weight_bytes -= sum(t.numel() * t.element_size() for t in (
+                    engine.model.embedding.table, getattr(engine.model.embedding, "bigram", None))
+                    if t is not None)
+                row["weights_read_gb"] = round(weight_bytes / 1e9, 2)
             ms = time_prefill(engine, T)
             row["prefill_2048_ms"] = round(ms, 3)
             row["prefill_tok_s"] = round(T * 1e3 / ms, 1)

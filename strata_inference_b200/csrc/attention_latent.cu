@@ -70,8 +70,9 @@ __device__ __forceinline__ void ldsm_x2_trans(uint32_t& r0, uint32_t& r1, const 
     asm volatile("ldmatrix.sync.aligned.m8n8.x2.trans.shared.b16 {%0,%1}, [%2];\n"
                  : "=r"(r0), "=r"(r1) : "r"(s));
 }
+// (not volatile: it touches registers only, so the compiler may place it among the loads)
 __device__ __forceinline__ void mma16816(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
-    asm volatile(
+    asm(
         "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 "
         "{%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
         : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
@@ -290,17 +291,21 @@ __global__ void __launch_bounds__(128) latent_attention_kernel(LatentArgs p) {
                 pa[kk][2] = pack2(pr[2 * kk + 1][0], pr[2 * kk + 1][1]);
                 pa[kk][3] = pack2(pr[2 * kk + 1][2], pr[2 * kk + 1][3]);
             }
-            // the weighted sum of this warp's columns (tiles warp, warp + 4, ... of 8 columns)
+            // the weighted sum of this warp's columns (tiles warp, warp + 4, ... of 8 columns);
+            // products that follow one another go to different accumulators
+            if (rescale) {
 #pragma unroll
-            for (int ti = 0; ti < NT; ++ti) {
-                const int nt = warp + 4 * ti;
-                if (nt < n_ntiles) {
-                    if (rescale) {
-                        o[ti][0] *= corr[0]; o[ti][1] *= corr[0];
-                        o[ti][2] *= corr[1]; o[ti][3] *= corr[1];
-                    }
+                for (int ti = 0; ti < NT; ++ti) {
+                    o[ti][0] *= corr[0]; o[ti][1] *= corr[0];
+                    o[ti][2] *= corr[1]; o[ti][3] *= corr[1];
+                }
+            }
 #pragma unroll
-                    for (int kk = 0; kk < KKT; ++kk) {
+            for (int kk = 0; kk < KKT; ++kk) {
+#pragma unroll
+                for (int ti = 0; ti < NT; ++ti) {
+                    const int nt = warp + 4 * ti;
+                    if (nt < n_ntiles) {
                         uint32_t b0, b1;
                         ldsm_x2_trans(b0, b1, kt + (size_t)(kk * 16 + (lane & 15)) * ldk + nt * 8);
                         mma16816(o[ti], pa[kk], b0, b1);
