@@ -17,7 +17,7 @@ import pytest
 import torch
 
 import plain_vavupel as plain
-from vavupel_cases import (ALONE, BROAD, MIXED, NARROW, ODD, SHARP, STRAIGHT, WIDE, assert_close, plain_logits, prompts,
+from vavupel_cases import (ALONE, BROAD, CORNERS, MIXED, NARROW, ODD, SHARP, STRAIGHT, WIDE, assert_close, plain_logits, prompts,
                            random_weights, rows_that_differ)
 
 pytestmark = pytest.mark.gpu
@@ -256,6 +256,24 @@ def test_other_sizes(name, dtype):
     for k in range(7):
         out = eng.step([(sa, [a[130 + k]]), (sb, [b[30 + k]])], [[0], [0]])
         assert_close(out, torch.stack([ra[130 + k], rb[30 + k]]), dtype, f"{name}: tokens {k}")
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("name", sorted(CORNERS))
+def test_corner_configurations(name, dtype):
+    """A prompt of 330 tokens (over five pages), then 30 single tokens, and a batch of three."""
+    cfg = CORNERS[name]
+    w = random_weights(cfg, seed=31)
+    eng = make_engine(cfg, w, dtype)
+    a, b, c = prompts(cfg, [360, 3, 90], seed=32)
+    ra, rb, rc = (plain_logits(cfg, w, t) for t in (a, b, c))
+    assert_close(run_portions(eng, a, [330] + [1] * 30), ra, dtype, f"{name}: prompt, then tokens")
+    slots = [eng.new_sequence() for _ in range(3)]
+    out = eng.step([(slots[0], a[:200]), (slots[1], b[:1]), (slots[2], c[:70])], [all_rows(200), [0], all_rows(70)])
+    assert_close(out, torch.cat([ra[:200], rb[:1], rc[:70]]), dtype, f"{name}: three prompts")
+    for k in range(2):
+        out = eng.step([(slots[0], [a[200 + k]]), (slots[1], [b[1 + k]]), (slots[2], [c[70 + k]])], [[0]] * 3)
+        assert_close(out, torch.stack([ra[200 + k], rb[1 + k], rc[70 + k]]), dtype, f"{name}: three tokens {k}")
 
 
 @pytest.mark.parametrize("dtype", DTYPES)

@@ -84,6 +84,18 @@ WIDE = model(128, 300, [
 # a latent row wider than 512 (the general attention kernel in both compute types)
 BROAD = model(64, 100, [latent(2, 16, 32, 16, 560, 50, ff=32), retention(1, 16, 16, [0.99])])
 
+# corners: a window of one (a row sees itself and the sink), a window longer than any request, 40 heads
+# in chunks of 16, a latent of 8 with 2 rotated columns, values wider than keys, a loop of one layer walked
+# four times, no feed-forward anywhere, a one-layer model whose only layer is looped
+CORNERS = {
+    "window_of_one": model(48, 90, [latent(2, 8, 4, 8, 12, 1), retention(2, 8, 3, [0.9, 0.99])], loop=(0, 2, 2)),
+    "long_window": model(48, 90, [latent(5, 8, 4, 12, 16, 5000, ff=24)], cap=0),
+    "many_heads": model(64, 90, [latent(40, 8, 8, 8, 24, 70), retention(20, 8, 8, [1.0 - 0.5 ** (i % 9 + 1) for i in range(20)])]),
+    "tiny_latent": model(32, 50, [latent(7, 24, 2, 40, 8, 37, ff=20), latent(2, 4, 2, 4, 8, 9)], loop=(1, 2, 4)),
+    "bare": model(40, 60, [retention(2, 8, 12, [0.97, 0.9]), latent(2, 8, 4, 8, 12, 20), retention(1, 16, 8, [0.999])],
+                  loop=(0, 1, 3), scale=0.25, buckets=1, mul_prev=0, mul_cur=1),
+}
+
 # no loop at all
 STRAIGHT = model(64, 150, [retention(2, 16, 16, [0.9, 0.99], ff=32), latent(2, 16, 8, 16, 24, 30, ff=32)])
 
