@@ -283,6 +283,7 @@ struct TcArgs {
     int n_heads, n_kv;
     int window;
     float scale, softcap;
+    const float* sink;       // [n_heads] or null: e^{sink_h} joins each row's denominator
 };
 
 // SPLIT.  When the grid is small against the device, a block (or pair) of query rows with
@@ -646,6 +647,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map, TcArgs p,
         float w_mine = 1.f, w_theirs = 0.f;
         const float* theirs = nullptr;       // the other half's accumulator columns of this thread
         float l_all = l + l_other;
+        float base = m_ref;                  // what the sums and the accumulator are relative to
         if (ok && is_split) {
             // the block's two partial results
             float* mine = p.part + (unit * 2 + part) * part_floats<HD>();
@@ -680,9 +682,13 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map, TcArgs p,
                 w_mine = m_ref == -INFINITY ? 0.f : exp2_fast(m_ref - top);
                 w_theirs = m_b == -INFINITY ? 0.f : exp2_fast(m_b - top);
                 l_all = w_mine * l_all + w_theirs * l_b;
+                base = top;
             }
         }
         if (ok) {
+            // a sink: one more term of the denominator, with no key and no value (too large a
+            // one gives an infinite sum and therefore a row of zeros, which is its limit)
+            if (p.sink != nullptr && l_all > 0.f) l_all += exp2_fast(p.sink[head] * LOG2E - base);
             const float inv = l_all > 0.f ? 1.0f / l_all : 0.f;
             const bool store = pos < n && pos >= q0;
             __nv_bfloat16* dst = p.out + (size_t)(row0 + pos) * p.n_heads * HD + (size_t)head * HD +
@@ -1025,8 +1031,9 @@ SIB_EXPORT int sib_attention_prefill_tc(const void* qkv, int width, int total_ro
                                         float scale, float softcap, int window, void* scratch,
                                         long long scratch_bytes, int* tickets, int n_tickets,
                                         const int* host_lens, const int* seq_q0, const int* host_q0,
-                                        void* stream) {
+                                        const float* sink, void* stream) {
     if (n_seqs == 0 || max_len == 0) return 0;
+    SIB_REQUIRE(sink == nullptr || softcap == 0.f, "attention_prefill_tc: a sink together with a cap is not built");
     SIB_REQUIRE(sib_attention_prefill_tc_supports(n_heads, n_kv, head_dim, width),
                 "attention_prefill_tc: heads=%d kv_heads=%d head_dim=%d is not a shape this kernel "
                 "takes (1 or 2 heads per kv head; head_dim 64, 128 or 256)", n_heads, n_kv, head_dim);
@@ -1083,7 +1090,7 @@ SIB_EXPORT int sib_attention_prefill_tc(const void* qkv, int width, int total_ro
     }
     if (items.n > 0) split_tiles = 0;
     TcArgs p{(__nv_bfloat16*)out, seq_row0, seq_len, seq_q0, error_flag, (float*)scratch, tickets,
-             split_tiles, n_heads, n_kv, window, scale, softcap};
+             split_tiles, n_heads, n_kv, window, scale, softcap, sink};
     cudaStream_t s = (cudaStream_t)stream;
 #define BY_G(HD, PAIR)                                                         \
     do {                                                                       \

@@ -255,6 +255,7 @@ __global__ void __launch_bounds__(128) latent_prepare_kernel(LatentPrepareArgs p
     pdl_wait();
     const T* row = (const T*)p.proj + (size_t)r * p.proj_stride;
     if (unit < p.n_heads) {
+        if (p.q_lat == nullptr) return;      // (the caller wants the key rows only)
         const T* lat = (const T*)p.q_lat + ((size_t)unit * p.rows + r) * p.rank;
         const T* part = row + (size_t)unit * (p.qd + p.rd) + p.qd;
         T* out = (T*)p.q_rows + ((size_t)r * p.n_heads + unit) * p.pad;
@@ -312,7 +313,8 @@ SIB_EXPORT int sib_latent_prepare(
                 qd, rd, rank, pad);
     SIB_REQUIRE(rot >= 0 && rot % 2 == 0 && rot <= rd && (rot == 0 || inv_freq != nullptr),
                 "latent_prepare: %d rotated dimensions of %d", rot, rd);
-    SIB_REQUIRE(row_pos && c_gain && q_lat && q_rows && k_rows, "latent_prepare: an argument is missing");
+    SIB_REQUIRE(row_pos && c_gain && k_rows && (q_lat != nullptr) == (q_rows != nullptr),
+                "latent_prepare: an argument is missing");
     SIB_REQUIRE(k_pool == nullptr || (page_table && row_seq && seq_slot && seq_end && page_tokens > 0 &&
                                       max_pages > 0),
                 "latent_prepare: incomplete cache description");
@@ -323,4 +325,78 @@ SIB_EXPORT int sib_latent_prepare(
     SIB_DISPATCH_DTYPE(dtype, sib_launch_chained(latent_prepare_kernel<T>, dim3(rows, (n_heads + 4) / 4),
                                                  dim3(128), 0, (cudaStream_t)stream, p));
     return sib_check_launch("latent_prepare");
+}
+
+// ---------------------------------------------------------------------------
+// latent_expand: packed rows for the prompt attention kernels when keys and values are
+// made per head from the latent (k_h = U_h c and v_h = V_h c, the caller's products):
+//   query head h:  [a_h (qd) | its last rd columns rotated | 0]
+//   key head h:    [k_h (qd) | the row's shared rotated part, as latent_prepare left it in
+//                   k_rows[r, rank : rank + rd] | 0]
+//   value head h:  [v_h (vd) | 0]
+// every head `hw` wide: qkv[r] = queries | keys | values.  One warp per (row, unit).
+// ---------------------------------------------------------------------------
+struct LatentExpandArgs {
+    const void* proj;          // [rows, proj_stride]: query heads of (qd + rd) | ...
+    const void* k_rows;        // [rows, pad]
+    const void* k_heads;       // [rows, n_heads * qd]
+    const void* v_heads;       // [rows, n_heads * vd]
+    void* qkv;                 // [rows, 3 * n_heads * hw]
+    const float* inv_freq;
+    const int* row_pos;
+    long long proj_stride;
+    int rows, n_heads, qd, rd, vd, rank, pad, hw, rot;
+};
+
+template <typename T>
+__global__ void __launch_bounds__(128) latent_expand_kernel(LatentExpandArgs p) {
+    pdl_trigger();
+    const int lane = threadIdx.x & 31;
+    const int r = blockIdx.x;
+    const int unit = blockIdx.y * 4 + (threadIdx.x >> 5);
+    if (unit >= 3 * p.n_heads) return;
+    const float pos = (float)p.row_pos[r];
+    const int rot = p.inv_freq ? p.rot : 0;
+    pdl_wait();
+    const int kind = unit / p.n_heads, h = unit % p.n_heads;
+    T* out = (T*)p.qkv + ((size_t)r * 3 * p.n_heads + unit) * p.hw;
+    const T zero = from_f32<T>(0.f);
+    if (kind == 0) {
+        const T* head = (const T*)p.proj + (size_t)r * p.proj_stride + (size_t)h * (p.qd + p.rd);
+        for (int d = lane; d < p.hw; d += 32) {
+            T y = zero;
+            if (d < p.qd) y = head[d];
+            else if (d < p.qd + p.rd) y = from_f32<T>(rotated_pair<T>(head + p.qd, d - p.qd, rot, p.inv_freq, pos));
+            out[d] = y;
+        }
+    } else if (kind == 1) {
+        const T* kh = (const T*)p.k_heads + ((size_t)r * p.n_heads + h) * p.qd;
+        const T* shared = (const T*)p.k_rows + (size_t)r * p.pad + p.rank;
+        for (int d = lane; d < p.hw; d += 32)
+            out[d] = d < p.qd ? kh[d] : (d < p.qd + p.rd ? shared[d - p.qd] : zero);
+    } else {
+        const T* vh = (const T*)p.v_heads + ((size_t)r * p.n_heads + h) * p.vd;
+        for (int d = lane; d < p.hw; d += 32) out[d] = d < p.vd ? vh[d] : zero;
+    }
+}
+
+SIB_EXPORT int sib_latent_expand(const void* proj, long long proj_stride, const void* k_rows,
+                                 const void* k_heads, const void* v_heads, void* qkv, int dtype,
+                                 const float* inv_freq, int rot, const int* row_pos, int rows,
+                                 int n_heads, int qd, int rd, int vd, int rank, int pad, int hw,
+                                 void* stream) {
+    if (rows == 0) return 0;
+    SIB_REQUIRE(rows > 0 && n_heads > 0 && qd > 0 && rd >= 0 && vd > 0 && hw >= qd + rd && hw >= vd &&
+                    pad >= rank + rd,
+                "latent_expand: rows=%d heads=%d widths %d + %d and %d in heads of %d", rows, n_heads, qd,
+                rd, vd, hw);
+    SIB_REQUIRE(rot >= 0 && rot % 2 == 0 && rot <= rd && (rot == 0 || inv_freq != nullptr),
+                "latent_expand: %d rotated dimensions of %d", rot, rd);
+    SIB_REQUIRE(proj && k_rows && k_heads && v_heads && qkv && row_pos, "latent_expand: an argument is missing");
+    SIB_REQUIRE((3 * n_heads + 3) / 4 < 65536, "latent_expand: too many heads (%d)", n_heads);
+    LatentExpandArgs p{proj, k_rows, k_heads, v_heads, qkv, rot ? inv_freq : nullptr, row_pos, proj_stride,
+                       rows, n_heads, qd, rd, vd, rank, pad, hw, rot};
+    SIB_DISPATCH_DTYPE(dtype, sib_launch_chained(latent_expand_kernel<T>, dim3(rows, (3 * n_heads + 3) / 4),
+                                                 dim3(128), 0, (cudaStream_t)stream, p));
+    return sib_check_launch("latent_expand");
 }

@@ -588,12 +588,17 @@ def latent_prepare(proj: torch.Tensor, q_lat: torch.Tensor, q_rows: torch.Tensor
     """Between the projections and the attention over a shared latent (csrc/head_prepare.cu):
     ``proj`` rows hold the query heads (``q_dim`` + ``rot_dim`` each) and then the down
     projection (``rank`` + ``rot_dim``); ``q_lat`` ``[heads, rows, rank]`` are the queries
-    already multiplied into the latent's space.  Writes ``q_rows`` ``[rows, heads * pad]``,
-    ``k_rows`` ``[rows, pad]`` and the cache cells of the rows."""
+    already multiplied into the latent's space.  Writes ``q_rows`` ``[rows, heads * pad]``
+    (not with ``q_lat`` and ``q_rows`` None), ``k_rows`` ``[rows, pad]`` and the cache cells of
+    the rows."""
     rows = proj.shape[0]
     _want(proj, proj.dtype, "proj", contiguous=False)
+    if (q_lat is None) != (q_rows is None):
+        raise KernelError("latent_prepare: q_lat and q_rows come together (None: the key rows only)")
     for t, shape, nm in ((q_lat, (n_heads, rows, rank), "q_lat"), (q_rows, (rows, n_heads * pad), "q_rows"),
                          (k_rows, (rows, pad), "k_rows")):
+        if t is None:
+            continue
         _want(t, proj.dtype, nm)
         if tuple(t.shape) != shape:
             raise KernelError(f"latent_prepare: {nm} must be {shape}")
@@ -614,6 +619,34 @@ def latent_prepare(proj: torch.Tensor, q_lat: torch.Tensor, q_rows: torch.Tensor
         _ptr(ctx.row_pos), _ptr(ctx.row_seq), _ptr(ctx.seq_slot), _ptr(ctx.seq_end), _ptr(k_pool),
         _ptr(page_table), c_int(max_pages), c_int(page_tokens), c_int(ring_tokens), c_int(rows),
         c_int(n_heads), c_int(q_dim), c_int(rot_dim), c_int(rank), c_int(pad), _stream()))
+
+
+@_timed(lambda proj, k_rows, k_heads, v_heads, qkv, *a, **kw: ("latent_expand", _nbytes(k_heads, v_heads, qkv) * 1.3, 0))
+def latent_expand(proj: torch.Tensor, k_rows: torch.Tensor, k_heads: torch.Tensor, v_heads: torch.Tensor,
+                  qkv: torch.Tensor, inv_freq: Optional[torch.Tensor], rot: int, row_pos, n_heads: int,
+                  q_dim: int, rot_dim: int, value_dim: int, rank: int, pad: int, head_width: int) -> torch.Tensor:
+    """Packed rows for the prompt attention kernels from keys and values made per head
+    (csrc/head_prepare.cu): ``qkv[r]`` = query heads ``[unrotated | rotated | 0]``, key heads
+    ``[k_heads | the row's shared rotated part (from k_rows) | 0]``, value heads ``[v_heads | 0]``,
+    every head ``head_width`` wide."""
+    rows = proj.shape[0]
+    _want(proj, proj.dtype, "proj", contiguous=False)
+    for t, shape, nm in ((k_rows, (rows, pad), "k_rows"), (k_heads, (rows, n_heads * q_dim), "k_heads"),
+                         (v_heads, (rows, n_heads * value_dim), "v_heads"),
+                         (qkv, (rows, 3 * n_heads * head_width), "qkv")):
+        _want(t, proj.dtype, nm)
+        if tuple(t.shape) != shape:
+            raise KernelError(f"latent_expand: {nm} must be {shape}")
+    if proj.stride(1) != 1 or proj.shape[1] < n_heads * (q_dim + rot_dim):
+        raise KernelError("latent_expand: a projected row must hold the query heads")
+    if rot:
+        _f32(inv_freq, rot // 2, "inv_freq")
+    _check(library().sib_latent_expand(
+        _ptr(proj), c_longlong(proj.stride(0)), _ptr(k_rows), _ptr(k_heads), _ptr(v_heads), _ptr(qkv),
+        _code(proj.dtype), _ptr(inv_freq if rot else None), c_int(rot), _ptr(row_pos), c_int(rows),
+        c_int(n_heads), c_int(q_dim), c_int(rot_dim), c_int(value_dim), c_int(rank), c_int(pad),
+        c_int(head_width), _stream()))
+    return qkv
 
 
 def _f32(t: Optional[torch.Tensor], n: int, name: str) -> None:
@@ -1005,7 +1038,7 @@ def attention_prefill_tc_plan(lens: Sequence[int], n_heads: int, n_kv: int, head
 
 @_timed(lambda qkv, out, seq_row0, seq_len, n_seqs, max_len, n_heads, n_kv, head_dim, scale,
         softcap, window, scratch=None, tickets=None, host_lens=None, seq_q0=None,
-        host_q0=None: _prompt_work(
+        host_q0=None, sink=None: _prompt_work(
             "attention_prefill_tc (tcgen05)", qkv, seq_len, n_heads, head_dim, window))
 def attention_prefill_tc(qkv: torch.Tensor, out: torch.Tensor, seq_row0, seq_len, n_seqs: int,
                          max_len: int, n_heads: int, n_kv: int, head_dim: int, scale: float,
@@ -1013,8 +1046,10 @@ def attention_prefill_tc(qkv: torch.Tensor, out: torch.Tensor, seq_row0, seq_len
                          tickets: Optional[torch.Tensor] = None,
                          host_lens: Optional[Sequence[int]] = None,
                          seq_q0: Optional[torch.Tensor] = None,
-                         host_q0: Optional[Sequence[int]] = None) -> torch.Tensor:
-    """The prompt attention on tcgen05 (see csrc/attention_prefill_tc.cu).  With ``scratch``
+                         host_q0: Optional[Sequence[int]] = None,
+                         sink: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """The prompt attention on tcgen05 (see csrc/attention_prefill_tc.cu).  ``sink``: one 32-bit
+    value per head whose exponential joins every row's denominator (no cap then).  With ``scratch``
     and ``tickets`` (int32, zero before the first call; every call leaves them zero) of the
     sizes ``attention_prefill_tc_split`` gives, a launch that cannot fill the device runs its
     long blocks of query rows as two halves.  With ``host_lens`` (the prompts' lengths, as
@@ -1029,6 +1064,8 @@ def attention_prefill_tc(qkv: torch.Tensor, out: torch.Tensor, seq_row0, seq_len
         raise KernelError("attention_prefill_tc: out must be [rows, heads * head_dim]")
     if tickets is not None:
         _want(tickets, torch.int32, "tickets")
+    if sink is not None:
+        _f32(sink, n_heads, "sink")
     _check(library().sib_attention_prefill_tc(
         _ptr(qkv), c_int(qkv.shape[1]), c_int(qkv.shape[0]), _ptr(out), _ptr(seq_row0),
         _ptr(seq_len), c_int(n_seqs), c_int(max_len), c_int(n_heads), c_int(n_kv), c_int(head_dim),
@@ -1038,7 +1075,7 @@ def attention_prefill_tc(qkv: torch.Tensor, out: torch.Tensor, seq_row0, seq_len
         None if host_lens is None else (c_int * len(host_lens))(*[int(n) for n in host_lens]),
         _ptr(seq_q0),
         None if host_q0 is None else (c_int * len(host_q0))(*[int(n) for n in host_q0]),
-        _stream()))
+        _ptr(sink), _stream()))
     return out
 
 

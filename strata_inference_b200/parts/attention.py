@@ -65,6 +65,9 @@ _USE_TCGEN05_PREFILL = os.environ.get("SIB_PREFILL_TCGEN05", "1") != "0"
 # SIB_LATENT_MMA=0 sends the bfloat16 latent attention to the general kernel instead of the
 # tensor-core one
 _USE_LATENT_MMA = os.environ.get("SIB_LATENT_MMA", "1") != "0"
+# SIB_LATENT_EXPAND=0: long bfloat16 prompts of the latent attention attend over the latent rows
+# too, instead of over keys and values made per head (the tcgen05 prompt kernel)
+_USE_LATENT_EXPAND = os.environ.get("SIB_LATENT_EXPAND", "1") != "0"
 
 
 def decode_shape(units: int, longest: int, window: int, resident4: int, resident8: int,
@@ -554,8 +557,12 @@ class LatentAttention:
         self.w_in = rt.cast_matrix(weights["in_proj.weight"])
         self.c_gain = weights["dkv_norm.gain"]
         # per head: U_h [qd, rank] (q times it) and V_h^T [rank, vd] (the summed latents times it)
-        self.w_uk = rt.cast_matrix(weights["uk_proj.weight"]).view(self.nh, self.qd, self.rank)
-        self.w_uv_t = rt.cast_matrix(weights["uv_proj.weight"]).view(self.nh, self.vd, self.rank).transpose(1, 2)
+        w_uk, w_uv = rt.cast_matrix(weights["uk_proj.weight"]), rt.cast_matrix(weights["uv_proj.weight"])
+        self.w_uk = w_uk.view(self.nh, self.qd, self.rank)
+        self.w_uv_t = w_uv.view(self.nh, self.vd, self.rank).transpose(1, 2)
+        self.w_uk_flat, self.w_uv_flat = w_uk, w_uv      # [heads * qd, rank], [heads * vd, rank]
+        # the head width of the prompt kernels that holds a key (unrotated and rotated part) and a value
+        self.hw = next((w for w in (64, 128, 256) if w >= max(self.qd + self.rd, self.vd)), 0)
         self.w_o = rt.cast_matrix(weights["o_proj.weight"])
         self.sink = weights.get("sink")
         self._target_warps = _WARPS_PER_SM * rt.sm_count
@@ -582,6 +589,43 @@ class LatentAttention:
         want = max(1, (2 * self.rt.sm_count) // max(1, tiles))
         return max(1, min(want, -(-longest // 64), 128))
 
+    def _attend_expanded(self, proj: torch.Tensor, ctx, view) -> torch.Tensor:
+        """Long prompts in bfloat16: the latent rows are normed, rotated and cached as ever, and
+        for the step's own rows keys and values are made per head (k_h = U_h c, v_h = V_h c:
+        two library products) and attended over by the tcgen05 prompt kernel, with the sink as
+        one more term of its last division: a third of the operations of the scores against
+        the latent, on the faster tensor-core path.  Later steps read the cached latent rows."""
+        rt, nh, qd, rd, vd, rank, kw, hw = self.rt, self.nh, self.qd, self.rd, self.vd, self.rank, self.kw, self.hw
+        R = proj.shape[0]
+        k_rows = torch.empty((R, kw), dtype=proj.dtype, device=proj.device)
+        native.latent_prepare(proj, None, None, k_rows, self.c_gain, self.eps, self.inv_freq, self.rot,
+                              ctx, view.k, view.page_table, view.page_tokens, view.ring_tokens, nh, qd, rd,
+                              rank, kw)
+        c_rows = k_rows[:, :rank]
+        with native.profile_region("library product (latent rows to keys and values)",
+                                   (nh * (qd + vd) * rank + R * (rank + nh * (qd + vd))) * proj.element_size(),
+                                   2.0 * R * nh * (qd + vd) * rank):
+            k_heads = torch.matmul(c_rows, self.w_uk_flat.t())
+            v_heads = torch.matmul(c_rows, self.w_uv_flat.t())
+        qkv = torch.empty((R, 3 * nh * hw), dtype=proj.dtype, device=proj.device)
+        native.latent_expand(proj, k_rows, k_heads, v_heads, qkv, self.inv_freq, self.rot, ctx.row_pos,
+                             nh, qd, rd, vd, rank, kw, hw)
+        out = torch.empty((R, nh * hw), dtype=proj.dtype, device=proj.device)
+        lens = None if ctx.graph_capture else ctx.counts
+        n_items = 0
+        if lens is not None:
+            n_items, need, n_tickets = native.attention_prefill_tc_plan(lens, nh, nh, hw, self.window)
+        if n_items == 0:
+            lens = None
+            need, n_tickets = native.attention_prefill_tc_split(ctx.n_seqs, ctx.max_count, nh, nh, hw)
+        native.attention_prefill_tc(qkv, out, ctx.seq_row0, ctx.seq_end, ctx.n_seqs, ctx.max_count, nh, nh,
+                                    hw, self.scale, 0.0, self.window, rt.scratch(need) if need else None,
+                                    rt.tickets(n_tickets) if need else None, lens, sink=self.sink)
+        vals = torch.empty((R, nh * vd), dtype=out.dtype, device=out.device)
+        gate = proj[:, self.n_q + rank + rd:self.n_q + rank + rd + nh] if self.head_gate else None
+        native.head_gate(out, gate, vals, nh, vd, hw)
+        return rt.linear(vals, self.w_o)
+
     def forward(self, x: torch.Tensor, ctx, entry: int, cache_entry: int,
                 owns_cache: bool) -> torch.Tensor:
         if not owns_cache:
@@ -600,6 +644,10 @@ class LatentAttention:
                         f"in a ring of {view.ring_tokens}; got {n}")
         proj = rt.linear(x, self.w_in)
         rt.flush()
+        if (fresh and proj.dtype == torch.bfloat16 and _USE_LATENT_EXPAND and _USE_TCGEN05_PREFILL
+                and self.hw and self.scale > 0 and ctx.max_count > rt.short_prompt_tokens
+                and native.attention_prefill_tc_supports(nh, nh, self.hw, 3 * nh * self.hw)):
+            return self._attend_expanded(proj, ctx, view)
         # the unrotated query columns of every head into the latent's space: [heads, rows, rank]
         q_heads = proj[:, :self.n_q].view(R, nh, qd + rd)[:, :, :qd].transpose(0, 1)
         with native.profile_region("library product (queries into the latent space)",

@@ -490,3 +490,73 @@ def test_tensor_core_latent_attention_alone(heads, kw, window):
                                 page_tokens, 0, ctx, out, scratch, sink.cuda(), heads, kw, scale, window, splits)
         err = (out.cpu().double().view(4, heads, kw) - ref).abs().max().item()
         assert err <= 2e-2 * ref.abs().max().item(), f"cache, {splits} runs: {err:.3e}"
+
+
+@pytest.mark.parametrize("heads, hd, window, lens", [(4, 64, 0, [200, 5, 64, 131, 300]), (6, 128, 96, [402, 130]),
+                                                     (16, 256, 700, [1100, 70]), (2, 128, 0, [2000])])
+def test_tcgen05_prompt_kernel_with_sinks(heads, hd, window, lens):
+    """The prompt kernel with one sink per head (a term of the denominator with no key and no
+    value) against a 64-bit softmax: as a grid, as a balanced list of work, and with long blocks
+    split in two.  Scores are spread widely, so single keys carry a row; some sinks are far
+    above the scores, some far below."""
+    from strata_inference_b200.kernels import native
+    g = torch.Generator().manual_seed(heads + hd)
+    scale = 3.0 / math.sqrt(hd)
+    sink = torch.randn(heads, generator=g) * 3.0 + 2.0
+    rows, refs = [], []
+    for T in lens:
+        q, k, v = (torch.randn((T, heads, hd), generator=g).to(torch.bfloat16) for _ in range(3))
+        s = torch.einsum("thd,jhd->htj", q.double(), k.double()) * scale
+        pos = torch.arange(T)
+        hidden = (pos[None, :] > pos[:, None]) | ((pos[:, None] - pos[None, :] >= window) if window else False)
+        s = s.masked_fill(hidden[None], float("-inf"))
+        top = torch.maximum(s.amax(-1), sink.double()[:, None])
+        e = torch.exp(s - top[..., None])
+        w = e / (e.sum(-1) + torch.exp(sink.double()[:, None] - top))[..., None]
+        refs.append(torch.einsum("htj,jhd->thd", w, v.double()))
+        rows.append(torch.cat([q.reshape(T, -1), k.reshape(T, -1), v.reshape(T, -1)], dim=1))
+    packed = torch.cat(rows).contiguous().cuda()
+    row0 = [sum(lens[:i]) for i in range(len(lens))]
+    i32 = lambda x: torch.tensor(x, dtype=torch.int32, device="cuda")  # noqa: E731
+    ref = torch.cat(refs).reshape(sum(lens), -1)
+
+    def run(scratch, tickets, host_lens):
+        out = torch.full((sum(lens), heads * hd), float("nan"), dtype=torch.bfloat16, device="cuda")
+        native.attention_prefill_tc(packed, out, i32(row0), i32(lens), len(lens), max(lens), heads, heads, hd,
+                                    scale, 0.0, window, scratch, tickets, host_lens, sink=sink.cuda())
+        assert native.attention_prefill_tc_error() == 0
+        err = (out.cpu().double() - ref).abs().max().item()
+        assert err <= 2e-2 * ref.abs().max().item(), f"{err:.3e} of {ref.abs().max().item():.3e}"
+    run(None, None, None)
+    need, n_tickets = native.attention_prefill_tc_split(len(lens), max(lens), heads, heads, hd)
+    if need:
+        run(torch.empty(need, dtype=torch.uint8, device="cuda"), torch.zeros(n_tickets, dtype=torch.int32, device="cuda"), None)
+    n_items, need, n_tickets = native.attention_prefill_tc_plan(lens, heads, heads, hd, window)
+    if n_items:
+        run(torch.empty(max(need, 16), dtype=torch.uint8, device="cuda"),
+            torch.zeros(max(n_tickets, 1), dtype=torch.int32, device="cuda"), lens)
+
+
+@pytest.mark.parametrize("name", ["mixed", "wide"])
+def test_long_prompts_through_keys_and_values_per_head_and_through_the_latent_agree(name):
+    """bfloat16 prompts of more than 128 tokens make keys and values per head for the tcgen05
+    prompt kernel; with that switched off they attend over the latent rows as single tokens do.
+    Both agree with the plain model, and with each other more closely than either must."""
+    from strata_inference_b200.parts import attention
+    cfg = {"mixed": MIXED, "wide": WIDE}[name]
+    w = random_weights(cfg, seed=41)
+    a, b = prompts(cfg, [300, 190], seed=42)
+    ref = torch.cat([plain_logits(cfg, w, a), plain_logits(cfg, w, b)])
+    got = {}
+    for expand in (True, False):
+        attention._USE_LATENT_EXPAND = expand
+        try:
+            eng = make_engine(cfg, w, "bfloat16")
+            sa, sb = eng.new_sequence(), eng.new_sequence()
+            got[expand] = eng.step([(sa, a), (sb, b)], [all_rows(300), all_rows(190)]).cpu().double()
+        finally:
+            attention._USE_LATENT_EXPAND = True
+        assert_close(got[expand], ref, "bfloat16", f"{name}, keys per head: {expand}")
+    diff = (got[True] - got[False]).abs().amax(-1) / ref.abs().max()
+    assert diff.median().item() <= 1.5e-2 and (diff > 4e-2).float().mean().item() <= 0.1, \
+        f"median {diff.median().item():.3e}, worst {diff.max().item():.3e}"
